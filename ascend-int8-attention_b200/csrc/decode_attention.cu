@@ -1,0 +1,1014 @@
+// INT8 shared-KV decode attention for sm_100a (C4: top-k compressed rows + window,
+// C128: every compressed row + window), eight heads, D = 512.
+//
+// Two launches per call, both on the caller's stream:
+//
+//   plan_kernel    one CTA.  Derives the live batch / token count from cuQ and seqLens
+//                  (trailing requests with seqLens <= 0 or cuQ < 0 are padding, as in the
+//                  reference's device code csrc/kernels/c8/attention_impl.h:121-137), counts
+//                  the 128-key tiles of every query token, cuts the flat tile list into one
+//                  contiguous range per CTA and writes the resulting work items, the per-CTA
+//                  item ranges and zeroed merge tickets into the workspace.
+//
+//   decode_kernel  one persistent CTA per SM, 9 warps:
+//                    warps 0-3  softmax / accumulate (thread = key for scores, = channel for outputs)
+//                    warps 4-7  producers: page-table lookups + 16-byte cp.async row gathers into a
+//                               3-stage ring of 128-key x 512-byte tiles (128-byte swizzled)
+//                    warp  8    one thread issues tcgen05.mma kind::i8 and commits to mbarriers
+//                  Per tile:  S[128 keys,16] = KV[128,512] . Qcodes[16,512]^T   (16 MMAs, K-major operands)
+//                             softmax in FP32 registers, P codes [128 keys,16] to shared memory
+//                             O[512,16]     = KV^T[512,128] . P[128,16]         (16 MMAs, MN-major operands;
+//                                             the SAME shared-memory tile serves both products)
+//                  Columns 0-7 of S / O belong to the high code plane of Q / P, 8-15 to the low
+//                  (residual) plane.  INT32 accumulators live in tensor memory and are converted to
+//                  FP32 once per tile, exactly as the CPU reference does per tile.
+//                  A token whose tiles span several CTAs is merged by the last CTA to finish a piece
+//                  (atomic ticket; nobody waits for another CTA).
+//
+// Arithmetic contract (npu_sparse_attn_sharedkv_int8/reference.py:268-322 of the reference):
+//   f = float(q) * scale_kind;  alpha = max(max|f| * (1/127), 1e-12);  n = clamp(f * (1/alpha), +-127)
+//   q_hi = rint(n), q_lo = rint((n - q_hi) * 127)
+//   logit = (float(S_hi) + float(S_lo) * (1/127)) * (alpha * softmax_scale); padded keys -> -1e30
+//   m' = max(m, max logit); r = exp(m - m'); w = exp(logit - m'); l = l r + sum w
+//   p_hi = rint(127 w), p_lo = rint((127 w - p_hi) * 127)
+//   acc = acc r + (float(O_hi) + float(O_lo) * (1/127)) * scale_kind * (1/127)
+//   state starts at m = sink, l = 1 (first piece) or 0;  out = bf16(sum g acc / sum g l), g = exp(m - max m)
+// Every FP32 operation is a separately rounded IEEE operation (no FMA contraction).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/sharedkv_c_abi.h"
+#include "ptx_sm100.cuh"
+#include "sharedkv_internal.h"
+
+namespace sharedkv {
+namespace {
+
+using namespace ptx;
+
+// ------------------------------------------------------------------ geometry
+constexpr uint32_t kHeads = 8, kDim = 512, kWindow = 128, kPage = 32;
+constexpr uint32_t kTileKeys = 128;
+constexpr uint32_t kStages = 3;
+constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
+constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
+constexpr uint32_t kThreads = 288;
+constexpr uint32_t kMaxCtas = 160;
+constexpr uint32_t kPlanThreads = 1024;
+constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
+constexpr float kInv127 = (float)(1.0 / 127);
+constexpr float kMasked = -1e30f;
+constexpr long long kWaitCycles = 4000000000ll;              // ~2 s: a wait that long is a failure, not a stall
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kSmKv = 0;
+constexpr uint32_t kSmQ = kSmKv + kStages * kTileBytes;      // 2 kinds x 16 rows x 512 B, swizzled
+constexpr uint32_t kSmP = kSmQ + 2 * 8192;                   // 2 buffers x 128 keys x 16 B
+constexpr uint32_t kSmScale = kSmP + 2 * 2048;               // FP32 [2][512]
+constexpr uint32_t kSmMask = kSmScale + 2 * 2048;            // UINT32 [stages][4]
+constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2][4 warps][8]
+constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [2 kinds][8]: alpha * softmax_scale
+constexpr uint32_t kSmBar = kSmAlpha + 64;                   // mbarriers
+constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kBarPReady = 10, kBarOFull = 12,
+                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17, kNumBars = 18;
+constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, ticket broadcast
+constexpr uint32_t kSmemBytes = kSmMisc + 16 + 1024;         // + alignment slack
+
+// tensor-memory columns
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0;     // S[b] at 16 b
+constexpr uint32_t kColO = 64;    // O[b] at 64 + 64 b, four 16-column channel blocks each
+
+// workspace map
+struct PlanHeader {
+    uint32_t live_batch, live_tokens, total_tiles, quota, n_items, status, grid, pad;
+};
+struct Item {
+    uint32_t token, batch;
+    int32_t position;
+    uint32_t tile_begin, tile_end, part, nparts, first_cta;
+};
+static_assert(sizeof(Item) == 32, "work item is two 16-byte loads");
+constexpr uint64_t kWsCtaFirst = 64;
+constexpr uint64_t kWsItems = 1024;
+__host__ __device__ inline uint64_t ws_tile_start(uint32_t tokens) { return kWsItems + 32ull * (tokens + kMaxCtas); }
+__host__ __device__ inline uint64_t ws_tickets(uint32_t tokens) { return ws_tile_start(tokens) + 4ull * tokens; }
+__host__ __device__ inline uint64_t ws_partials(uint32_t tokens)
+{
+    return (ws_tickets(tokens) + 4ull * tokens + 255ull) & ~255ull;
+}
+
+enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1 };
+
+// ------------------------------------------------------------------ small helpers
+__device__ __forceinline__ uint32_t tiles_of_token(int ratio, int32_t position, uint32_t topk)
+{
+    if (position < 0) return 1;
+    const uint32_t count = (uint32_t)(position + 1) / (uint32_t)ratio;
+    if (ratio == 4) return 1 + (count ? (topk + kTileKeys - 1) / kTileKeys : 0);
+    return 1 + (count + kTileKeys - 1) / kTileKeys;
+}
+
+__device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lane)
+{
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t n = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= (uint32_t)d) v += n;
+    }
+    return v;
+}
+
+// Exclusive prefix over the 1024 threads of the plan CTA; `total` receives the sum.
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *scratch, uint32_t &total)
+{
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t incl = warp_inclusive_scan(v, lane);
+    if (lane == 31) scratch[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t s = scratch[lane];
+        const uint32_t si = warp_inclusive_scan(s, lane);
+        scratch[32 + lane] = si - s;
+        if (lane == 31) scratch[64] = si;
+    }
+    __syncthreads();
+    const uint32_t result = incl - v + scratch[32 + warp];
+    total = scratch[64];
+    __syncthreads();
+    return result;
+}
+
+// ------------------------------------------------------------------ plan kernel
+template <int RATIO>
+__global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p, const uint32_t grid)
+{
+    __shared__ uint32_t scratch[80];
+    __shared__ uint32_t s_live;
+    const uint32_t tid = threadIdx.x;
+    const int32_t *cu = reinterpret_cast<const int32_t *>(p.cuQ);
+    const int32_t *seq = reinterpret_cast<const int32_t *>(p.seqLens);
+    char *ws = reinterpret_cast<char *>(p.workspace);
+    PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
+    uint32_t *cta_first = reinterpret_cast<uint32_t *>(ws + kWsCtaFirst);
+    Item *items = reinterpret_cast<Item *>(ws + kWsItems);
+    uint32_t *tile_start = reinterpret_cast<uint32_t *>(ws + ws_tile_start(p.tokens));
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
+
+    if (tid == 0) s_live = 0;
+    __syncthreads();
+    uint32_t live = 0;
+    for (uint32_t b = tid; b < p.batch; b += kPlanThreads)
+        if (seq[b] > 0 && cu[b + 1] >= 0) live = b + 1;
+    if (live) atomicMax(&s_live, live);
+    __syncthreads();
+    const uint32_t live_batch = s_live;
+    int32_t end = live_batch ? cu[live_batch] : 0;
+    const uint32_t live_tokens = end <= 0 ? 0u : ((uint32_t)end < p.tokens ? (uint32_t)end : p.tokens);
+
+    // pass 1: flat tile offset of every live token
+    uint32_t carry = 0;
+    for (uint32_t base = 0; base < live_tokens; base += kPlanThreads) {
+        const uint32_t t = base + tid;
+        uint32_t n = 0;
+        if (t < live_tokens) {
+            uint32_t lo = 0, hi = live_batch - 1;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (cu[mid + 1] <= (int32_t)t) lo = mid + 1; else hi = mid;
+            }
+            const int32_t position = seq[lo] - (cu[lo + 1] - (int32_t)t);
+            n = tiles_of_token(RATIO, position, p.topk);
+        }
+        uint32_t total;
+        const uint32_t offset = block_exclusive_scan(n, scratch, total);
+        if (t < live_tokens) tile_start[t] = carry + offset;
+        carry += total;
+    }
+    const uint32_t total_tiles = carry;
+    const uint32_t quota = total_tiles ? (total_tiles + grid - 1) / grid : 1;
+    for (uint32_t c = tid; c <= grid; c += kPlanThreads) cta_first[c] = 0xffffffffu;
+    __syncthreads();
+
+    // pass 2: cut tokens at CTA boundaries and emit items
+    uint32_t item_carry = 0;
+    for (uint32_t base = 0; base < live_tokens; base += kPlanThreads) {
+        const uint32_t t = base + tid;
+        uint32_t pieces = 0, start = 0, n = 0, batch = 0;
+        int32_t position = 0;
+        if (t < live_tokens) {
+            uint32_t lo = 0, hi = live_batch - 1;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (cu[mid + 1] <= (int32_t)t) lo = mid + 1; else hi = mid;
+            }
+            batch = lo;
+            position = seq[lo] - (cu[lo + 1] - (int32_t)t);
+            n = tiles_of_token(RATIO, position, p.topk);
+            start = tile_start[t];
+            pieces = (start + n - 1) / quota - start / quota + 1;
+            tickets[t] = 0;
+        }
+        uint32_t total;
+        const uint32_t offset = block_exclusive_scan(pieces, scratch, total);
+        if (t < live_tokens) {
+            const uint32_t c0 = start / quota;
+            for (uint32_t j = 0; j < pieces; ++j) {
+                const uint32_t c = c0 + j;
+                const uint32_t lo_flat = max(start, c * quota), hi_flat = min(start + n, (c + 1) * quota);
+                const uint32_t index = item_carry + offset + j;
+                Item it;
+                it.token = t; it.batch = batch; it.position = position;
+                it.tile_begin = lo_flat - start; it.tile_end = hi_flat - start;
+                it.part = j; it.nparts = pieces; it.first_cta = c0;
+                items[index] = it;
+                if (lo_flat == c * quota) cta_first[c] = index;
+            }
+        }
+        item_carry += total;
+    }
+    __syncthreads();
+    for (uint32_t c = tid; c <= grid; c += kPlanThreads)
+        if (cta_first[c] == 0xffffffffu) cta_first[c] = item_carry;
+    if (tid == 0) {
+        header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
+        header->quota = quota; header->n_items = item_carry; header->status = kStatusOk; header->grid = grid;
+        header->pad = 0;
+    }
+}
+
+// ------------------------------------------------------------------ decode kernel pieces
+struct Shared {
+    uint32_t base;              // shared-space address of the aligned region
+    char *ptr;                  // generic pointer to the same
+    __device__ __forceinline__ uint32_t bar(uint32_t i) const { return base + kSmBar + 8 * i; }
+    __device__ __forceinline__ volatile uint32_t *misc() const { return reinterpret_cast<volatile uint32_t *>(ptr + kSmMisc); }
+};
+
+// Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.
+__device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
+{
+    const uint32_t bar = sm.bar(bar_index);
+    if (mbar_try_wait(bar, parity)) return true;
+    volatile uint32_t *misc = sm.misc();
+    const long long start = clock64();
+#pragma unroll 1
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0) {
+            if (misc[1]) return false;
+            if (clock64() - start > kWaitCycles) { misc[1] = 1; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
+{
+    const uint4 *src = reinterpret_cast<const uint4 *>(items + index);
+    const uint4 a = src[0], b = src[1];
+    Item it;
+    it.token = a.x; it.batch = a.y; it.position = (int32_t)a.z; it.tile_begin = a.w;
+    it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
+    return it;
+}
+
+// Swizzled (128-byte) location of 16-byte chunk `chunk` (0..31) of row `row` in a
+// [4 segments][rows/8][8][128 B] tile whose segments are `seg_bytes` apart.
+__device__ __forceinline__ uint32_t tile_offset(uint32_t row, uint32_t chunk, uint32_t seg_bytes)
+{
+    const uint32_t seg = chunk >> 3, c = chunk & 7u, r = row & 7u;
+    return seg * seg_bytes + (row >> 3) * 1024u + r * 128u + ((c ^ r) << 4);
+}
+
+// Reduce eight per-thread values across the 32 lanes with max; afterwards lane 4 h (h = 0..7)
+// holds the warp-wide maximum of value h.  9 shuffles instead of 40.
+__device__ __forceinline__ float warp_max8(const float (&v)[8], uint32_t lane)
+{
+    float a[4], b[2], c;
+    const bool up16 = lane & 16u, up8 = lane & 8u, up4 = lane & 4u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float send = up16 ? v[i] : v[i + 4], keep = up16 ? v[i + 4] : v[i];
+        a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float send = up8 ? a[i] : a[i + 2], keep = up8 ? a[i + 2] : a[i];
+        b[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+    }
+    {
+        const float send = up4 ? b[0] : b[1], keep = up4 ? b[1] : b[0];
+        c = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+    }
+    c = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, 2));
+    c = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, 1));
+    return c;   // value index = 4*bit4 + 2*bit3 + bit2 of the lane
+}
+__device__ __forceinline__ float warp_sum8(const float (&v)[8], uint32_t lane)
+{
+    float a[4], b[2], c;
+    const bool up16 = lane & 16u, up8 = lane & 8u, up4 = lane & 4u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float send = up16 ? v[i] : v[i + 4], keep = up16 ? v[i + 4] : v[i];
+        a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float send = up8 ? a[i] : a[i + 2], keep = up8 ? a[i + 2] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    {
+        const float send = up4 ? b[0] : b[1], keep = up4 ? b[1] : b[0];
+        c = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+__device__ __forceinline__ uint32_t reduced_value_index(uint32_t lane)
+{
+    return ((lane >> 4) & 1u) * 4u + ((lane >> 3) & 1u) * 2u + ((lane >> 2) & 1u);
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
+{
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
+
+// ------------------------------------------------------------------ producer
+// Walks the CTA's tiles in order.  One cursor per pipeline stage of the producer.
+struct Cursor {
+    uint32_t item, items_end, j;
+    Item it;
+    bool done;
+};
+__device__ __forceinline__ void cursor_init(Cursor &c, const Item *items, uint32_t first, uint32_t end)
+{
+    c.item = first; c.items_end = end; c.done = first >= end;
+    if (!c.done) { c.it = load_item(items, first); c.j = c.it.tile_begin; }
+}
+// Returns true when the cursor moved on to a new item.
+__device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items)
+{
+    if (++c.j < c.it.tile_end) return false;
+    if (++c.item >= c.items_end) { c.done = true; return false; }
+    c.it = load_item(items, c.item);
+    c.j = c.it.tile_begin;
+    return true;
+}
+
+// Short-context C4 (fewer compressed rows than top-k slots): the valid selections are packed
+// to the front, order kept (reference.py:253).  Lane c keeps the validity mask of slots
+// [32 c, 32 c + 32) and the inclusive count up to and including its chunk.
+struct Compaction {
+    uint32_t mask, inclusive, total;
+    bool active;
+};
+__device__ __forceinline__ void compaction_build(Compaction &k, const SharedKVArgs &p, const Item &it, uint32_t lane)
+{
+    const uint32_t count = it.position < 0 ? 0u : (uint32_t)(it.position + 1) / 4u;
+    k.active = count < p.topk && p.topk <= 1024u;
+    if (!k.active) return;
+    const int32_t *ix = reinterpret_cast<const int32_t *>(p.indices) + (uint64_t)it.token * p.topk;
+    uint32_t mine = 0;
+    const uint32_t chunks = (p.topk + 31u) / 32u;
+#pragma unroll 8
+    for (uint32_t c = 0; c < chunks; ++c) {
+        const uint32_t s = c * 32u + lane;
+        int32_t v = -1;
+        if (s < p.topk) v = ix[s];
+        const uint32_t m = __ballot_sync(0xffffffffu, v >= 0 && (uint32_t)v < count);
+        if (lane == c) mine = m;
+    }
+    k.mask = mine;
+    k.inclusive = warp_inclusive_scan(__popc(mine), lane);
+    k.total = __shfl_sync(0xffffffffu, k.inclusive, 31);
+}
+// Slot (0..topk) holding the s-th valid selection; s < total.
+__device__ __forceinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s, bool in_range)
+{
+    uint32_t chunk = 0;
+#pragma unroll 8
+    for (int i = 0; i < 32; ++i) {
+        const uint32_t incl = __shfl_sync(0xffffffffu, k.inclusive, i);
+        chunk += (in_range && incl <= s) ? 1u : 0u;
+    }
+    chunk &= 31u;
+    const uint32_t m = __shfl_sync(0xffffffffu, k.mask, chunk);
+    const uint32_t incl = __shfl_sync(0xffffffffu, k.inclusive, chunk);
+    const uint32_t before = incl - __popc(m);
+    const uint32_t bit = in_range ? __fns(m, 0, (int)(s - before) + 1) : 0u;
+    return chunk * 32u + (bit & 31u);
+}
+
+// Stage A of the producer: logical row of this lane's slot in the cursor's tile (may read the
+// top-k index array).  Returns -1 for a slot that holds no key.
+template <int RATIO>
+__device__ __forceinline__ int32_t logical_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot)
+{
+    const Item &it = c.it;
+    if (it.position < 0) return -1;
+    if (c.j == 0) {
+        const uint32_t n = min((uint32_t)it.position + 1u, kWindow);
+        return slot < n ? (int32_t)((uint32_t)it.position + 1u - n + slot) : -1;
+    }
+    const uint32_t s = (c.j - 1u) * kTileKeys + slot;
+    const uint32_t count = (uint32_t)(it.position + 1) / (uint32_t)RATIO;
+    if (RATIO == 128) return s < count ? (int32_t)s : -1;
+    const int32_t *ix = reinterpret_cast<const int32_t *>(p.indices) + (uint64_t)it.token * p.topk;
+    if (k.active) {
+        const bool in_range = s < k.total;
+        const uint32_t src = compaction_slot(k, s, in_range);
+        return in_range ? ix[src] : -1;
+    }
+    if (s >= p.topk) return -1;
+    const int32_t v = ix[s];
+    return (v >= 0 && (uint32_t)v < count) ? v : -1;
+}
+
+template <int RATIO>
+__device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, uint32_t first, uint32_t end,
+                              uint32_t pw, uint32_t lane)
+{
+    Cursor ca, cb, cc;
+    cursor_init(ca, items, first, end);
+    cursor_init(cb, items, first, end);
+    cursor_init(cc, items, first, end);
+    Compaction comp;
+    comp.active = false; comp.mask = comp.inclusive = comp.total = 0;
+    if (RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
+
+    const int32_t *ori_table = reinterpret_cast<const int32_t *>(p.oriTable);
+    const int32_t *cmp_table = reinterpret_cast<const int32_t *>(p.cmpTable);
+    const uint32_t slot = pw * 32u + lane;
+    int32_t row_a = -1, row_b = -1;       // logical rows handed from stage A to B, B to C
+    int32_t page_b = 0;
+    uint32_t issued = 0;                  // tiles whose copies have been issued
+    uint32_t signalled = 0;               // tiles whose "full" barrier this thread has arrived on
+
+    for (uint32_t n = 0;; ++n) {
+        // ---- stage C inputs are last iteration's stage B outputs
+        const int32_t row_c = row_b, page_c = page_b;
+        // ---- stage B: page-table lookup for tile n-1
+        if (n >= 1 && !cb.done) {
+            row_b = row_a;
+            page_b = 0;
+            if (row_b >= 0) {
+                page_b = cb.j == 0 ? ori_table[(uint64_t)cb.it.batch * p.oriTableWidth + ((uint32_t)row_b >> 5)]
+                                   : cmp_table[(uint64_t)cb.it.batch * p.cmpTableWidth + ((uint32_t)row_b >> 5)];
+            }
+        }
+        // ---- stage A: logical row for tile n
+        if (!ca.done) row_a = logical_row<RATIO>(p, ca, comp, slot);
+        // ---- stage C: issue the copies of tile n-2
+        if (n >= 2) {
+            if (cc.done) break;
+            const uint32_t stage = issued % kStages, pass = issued / kStages;
+            if (!wait_phase(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
+            const bool ori = cc.j == 0;
+            bool valid = row_c >= 0;
+            if (valid && ori && (uint32_t)page_c >= p.oriPages) valid = false;   // never read outside the original cache
+            const uint64_t src = !valid ? 0ull
+                : (ori ? p.ori + (uint64_t)(uint32_t)page_c * p.oriStride : p.cmp + (uint64_t)(uint32_t)page_c * p.cmpStride)
+                  + (uint64_t)((uint32_t)row_c & 31u) * kDim;
+            const uint32_t mask = __ballot_sync(0xffffffffu, valid);
+            if (lane == 0) reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + pw] = mask;
+            const uint32_t tile = sm.base + kSmKv + stage * kTileBytes;
+            const uint32_t lo = (uint32_t)src, hi = (uint32_t)(src >> 32);
+#pragma unroll 4
+            for (uint32_t r = 0; r < 32u; ++r) {
+                if (!((mask >> r) & 1u)) continue;
+                const uint64_t rsrc = ((uint64_t)__shfl_sync(0xffffffffu, hi, r) << 32) | __shfl_sync(0xffffffffu, lo, r);
+                cp_async16(tile + tile_offset(pw * 32u + r, lane, kSegBytes), reinterpret_cast<const char *>(rsrc) + lane * 16u);
+            }
+            cp_async_commit();
+            ++issued;
+            if (issued - signalled == 2) {            // keep one tile in flight behind the newest
+                cp_async_wait<1>();
+                fence_proxy_async_smem();
+                mbar_arrive(sm.bar(kBarFull + signalled % kStages));
+                ++signalled;
+            }
+            cursor_advance(cc, items);
+        }
+        if (n >= 1 && !cb.done) cursor_advance(cb, items);
+        if (!ca.done) {
+            if (cursor_advance(ca, items) && RATIO == 4) compaction_build(comp, p, ca.it, lane);
+        }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    while (signalled < issued) {
+        mbar_arrive(sm.bar(kBarFull + signalled % kStages));
+        ++signalled;
+    }
+}
+
+// ------------------------------------------------------------------ MMA issuer (one thread)
+__device__ void mma_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+{
+    constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
+    constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
+    uint32_t gt = 0;                       // tiles issued (QK) so far
+    bool pending = false;                  // a tile whose PV has not been issued yet
+    uint32_t pending_gt = 0;
+
+    auto issue_pv = [&](uint32_t t) -> bool {
+        const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+        if (!wait_phase(sm, kBarPReady + buf, ph)) return false;
+        if (!wait_phase(sm, kBarOFree + buf, ph ^ 1u)) return false;
+        tc_fence_after();
+        const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+        const uint32_t pb = sm.base + kSmP + buf * 2048u;
+#pragma unroll
+        for (uint32_t mb = 0; mb < 4; ++mb) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+                const uint64_t a = smem_desc(kv + mb * kSegBytes + kk * 4096u, kSegBytes, 1024u, kSwizzle128);
+                const uint64_t b = smem_desc(pb + kk * 512u, 128u, 2048u, kSwizzleNone);
+                mma_i8(tmem + kColO + buf * 64u + mb * 16u, a, b, kIdescPV, kk);
+            }
+        }
+        mma_commit(sm.bar(kBarOFull + buf));
+        mma_commit(sm.bar(kBarEmpty + stage));
+        return true;
+    };
+
+    for (uint32_t k = first; k < end; ++k) {
+        const Item it = load_item(items, k);
+        if (!wait_phase(sm, kBarQReady, (k - first) & 1u)) return;
+        for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
+            const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
+            if (!wait_phase(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
+            if (!wait_phase(sm, kBarSFree + buf, ph ^ 1u)) return;
+            tc_fence_after();
+            const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+            const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : 8192u);
+#pragma unroll
+            for (uint32_t ks = 0; ks < 16; ++ks) {
+                const uint32_t seg = ks >> 2, part = ks & 3u;
+                const uint64_t a = smem_desc(kv + seg * kSegBytes + part * 32u, 16u, 1024u, kSwizzle128);
+                const uint64_t b = smem_desc(qb + seg * 2048u + part * 32u, 16u, 1024u, kSwizzle128);
+                mma_i8(tmem + kColS + buf * 16u, a, b, kIdescQK, ks);
+            }
+            mma_commit(sm.bar(kBarSFull + buf));
+            if (pending && !issue_pv(pending_gt)) return;
+            pending = true; pending_gt = gt;
+        }
+        if (pending) {
+            if (!issue_pv(pending_gt)) return;
+            pending = false;
+        }
+    }
+}
+
+// ------------------------------------------------------------------ softmax / accumulate warps
+// Synchronise the four softmax warps through an mbarrier (a wait here can time out, a bar.sync cannot).
+__device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t &phase)
+{
+    mbar_arrive(sm.bar(kBarGroup));
+    const bool ok = wait_phase(sm, kBarGroup, phase);
+    phase ^= 1u;
+    return ok;
+}
+
+template <int RATIO, bool DEBUG>
+__device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const PlanHeader *header,
+                             const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+{
+    const uint32_t tid = threadIdx.x;              // 0..127: key within a tile, channel within a 128-block
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
+    char *ws = reinterpret_cast<char *>(p.workspace);
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
+    float *partials = reinterpret_cast<float *>(ws + ws_partials(p.tokens));
+    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale);
+    float *red = reinterpret_cast<float *>(sm.ptr + kSmRed);
+    const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha);
+    volatile uint32_t *misc = sm.misc();
+    uint32_t group_phase = 0;
+
+    float sink[8];
+#pragma unroll
+    for (int h = 0; h < 8; ++h) sink[h] = reinterpret_cast<const float *>(p.sinks)[h];
+    float sc[2][4];                                // cache scales of this thread's four channels
+#pragma unroll
+    for (int kind = 0; kind < 2; ++kind)
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + tid];
+
+    // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
+    {
+        const uint32_t live = header->live_tokens;
+        for (uint32_t t = live + blockIdx.x; t < p.tokens; t += gridDim.x) {
+            uint4 *o = reinterpret_cast<uint4 *>(p.out) + (uint64_t)t * 512u;
+            for (uint32_t i = tid; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
+            if (p.lse && tid < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)t * 8u + tid] = 0.f;
+        }
+    }
+
+    uint32_t gt = 0;                               // tiles consumed so far by this CTA
+    for (uint32_t k = first; k < end; ++k) {
+        const Item it = load_item(items, k);
+
+        // ---------------- query encode: thread = (head, 32-channel slice)
+        {
+            const uint32_t h = tid >> 4, slice = tid & 15u, d0 = slice * 32u;
+            const uint4 *qsrc = reinterpret_cast<const uint4 *>(p.q + ((uint64_t)it.token * 8u + h) * 1024u + d0 * 2u);
+            uint4 raw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) raw[i] = __ldg(qsrc + i);
+            const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw);
+#pragma unroll
+            for (uint32_t kind = 0; kind < 2; ++kind) {
+                float f[32];
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float x0 = __uint_as_float(rw[i] << 16), x1 = __uint_as_float(rw[i] & 0xffff0000u);
+                    f[2 * i] = __fmul_rn(x0, scales[kind * 512 + d0 + 2 * i]);
+                    f[2 * i + 1] = __fmul_rn(x1, scales[kind * 512 + d0 + 2 * i + 1]);
+                    amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+                }
+#pragma unroll
+                for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+                const float alpha = fmaxf(__fmul_rn(amax, kInv127), 1e-12f);
+                const float rcp = __frcp_rn(alpha);
+                int hi[32], lo[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float nrm = fminf(fmaxf(__fmul_rn(f[i], rcp), -127.f), 127.f);
+                    const float hf = rintf(nrm);
+                    hi[i] = (int)hf;
+                    lo[i] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
+                }
+                char *qdst = sm.ptr + kSmQ + kind * 8192u;
+#pragma unroll
+                for (uint32_t c = 0; c < 2; ++c) {
+                    const uint4 vh = make_uint4(pack4(hi[16 * c], hi[16 * c + 1], hi[16 * c + 2], hi[16 * c + 3]),
+                                                pack4(hi[16 * c + 4], hi[16 * c + 5], hi[16 * c + 6], hi[16 * c + 7]),
+                                                pack4(hi[16 * c + 8], hi[16 * c + 9], hi[16 * c + 10], hi[16 * c + 11]),
+                                                pack4(hi[16 * c + 12], hi[16 * c + 13], hi[16 * c + 14], hi[16 * c + 15]));
+                    const uint4 vl = make_uint4(pack4(lo[16 * c], lo[16 * c + 1], lo[16 * c + 2], lo[16 * c + 3]),
+                                                pack4(lo[16 * c + 4], lo[16 * c + 5], lo[16 * c + 6], lo[16 * c + 7]),
+                                                pack4(lo[16 * c + 8], lo[16 * c + 9], lo[16 * c + 10], lo[16 * c + 11]),
+                                                pack4(lo[16 * c + 12], lo[16 * c + 13], lo[16 * c + 14], lo[16 * c + 15]));
+                    const uint32_t chunk = slice * 2u + c;
+                    *reinterpret_cast<uint4 *>(qdst + tile_offset(h, chunk, 2048u)) = vh;
+                    *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, chunk, 2048u)) = vl;
+                    if (DEBUG) {
+                        char *g = reinterpret_cast<char *>(dbg.qCodes) + ((uint64_t)it.token * 2u + kind) * 16u * 512u;
+                        *reinterpret_cast<uint4 *>(g + h * 512u + chunk * 16u) = vh;
+                        *reinterpret_cast<uint4 *>(g + (8u + h) * 512u + chunk * 16u) = vl;
+                    }
+                }
+                if (slice == 0) reinterpret_cast<float *>(sm.ptr + kSmAlpha)[kind * 8u + h] = __fmul_rn(alpha, p.softmaxScale);
+            }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(sm.bar(kBarQReady));
+        if (!group_sync(sm, group_phase)) return;
+
+        // ---------------- online softmax over this item's tiles
+        float m[8], l[8], r_prev[8], acc[4][8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+            m[h] = sink[h];
+            l[h] = (tid == 0 && it.tile_begin == 0) ? 1.f : 0.f;
+            r_prev[h] = 1.f;
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
+        }
+        bool have_prev = false;
+        uint32_t prev_gt = 0, prev_kind = 0, prev_rec = 0;
+
+        auto drain = [&](uint32_t t, uint32_t kind, uint32_t rec) -> bool {
+            const uint32_t buf = t & 1u, ph = (t >> 1) & 1u;
+            if (!wait_phase(sm, kBarOFull + buf, ph)) return false;
+            tc_fence_after();
+            uint32_t o[4][16];
+#pragma unroll
+            for (uint32_t mb = 0; mb < 4; ++mb) tmem_ld16(tmem_lane + kColO + buf * 64u + mb * 16u, o[mb]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(sm.bar(kBarOFree + buf));
+#pragma unroll
+            for (uint32_t mb = 0; mb < 4; ++mb) {
+                if (DEBUG && rec < dbg.maxTiles) {
+                    uint4 *g = reinterpret_cast<uint4 *>(dbg.pvAcc) + ((uint64_t)rec * 512u + mb * 128u + tid) * 4u;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[mb][4 * i], o[mb][4 * i + 1], o[mb][4 * i + 2], o[mb][4 * i + 3]);
+                }
+                const float s = kind ? sc[1][mb] : sc[0][mb];
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {
+                    const float dots = __fadd_rn((float)(int)o[mb][h], __fmul_rn((float)(int)o[mb][8 + h], kInv127));
+                    const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
+                    acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r_prev[h]), pv);
+                }
+            }
+            return true;
+        };
+
+        for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
+            const uint32_t kind = j == 0 ? 0u : 1u;
+            const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
+            if (!wait_phase(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
+            const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
+            const bool valid = (mask_word >> lane) & 1u;
+            if (!wait_phase(sm, kBarSFull + buf, ph)) return;
+            tc_fence_after();
+            uint32_t s[16];
+            tmem_ld16(tmem_lane + kColS + buf * 16u, s);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(sm.bar(kBarSFree + buf));
+
+            uint32_t rec = 0;
+            if (DEBUG) {
+                if (tid == 0) misc[2] = atomicAdd(reinterpret_cast<uint32_t *>(dbg.counter), 1u);
+                if (!group_sync(sm, group_phase)) return;
+                rec = misc[2];
+                if (rec < dbg.maxTiles) {
+                    if (tid == 0) {
+                        int32_t *info = reinterpret_cast<int32_t *>(dbg.tileInfo) + (uint64_t)rec * 4u;
+                        info[0] = (int32_t)it.token; info[1] = (int32_t)kind; info[2] = (int32_t)(kind ? j - 1u : 0u); info[3] = (int32_t)it.part;
+                    }
+                    if (lane == 0) reinterpret_cast<uint32_t *>(dbg.validMask)[(uint64_t)rec * 4u + warp] = mask_word;
+                    uint4 *g = reinterpret_cast<uint4 *>(dbg.qkAcc) + ((uint64_t)rec * 128u + tid) * 4u;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
+                }
+            }
+
+            float logit[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                const float dots = __fadd_rn((float)(int)s[h], __fmul_rn((float)(int)s[8 + h], kInv127));
+                logit[h] = valid ? __fmul_rn(dots, alphas[kind * 8u + h]) : kMasked;
+            }
+            const float wmax = warp_max8(logit, lane);
+            float *slot_red = red + (gt & 1u) * 32u;
+            if ((lane & 3u) == 0) slot_red[warp * 8u + reduced_value_index(lane)] = wmax;
+            if (!group_sync(sm, group_phase)) return;
+            float r[8];
+            int p_hi[8], p_lo[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                const float tmax = fmaxf(fmaxf(slot_red[h], slot_red[8 + h]), fmaxf(slot_red[16 + h], slot_red[24 + h]));
+                const float mnew = fmaxf(m[h], tmax);
+                r[h] = expf(__fsub_rn(m[h], mnew));
+                const float w = expf(__fsub_rn(logit[h], mnew));
+                l[h] = __fadd_rn(__fmul_rn(l[h], r[h]), w);
+                const float w127 = __fmul_rn(w, 127.f);
+                const float hf = rintf(w127);
+                p_hi[h] = (int)hf;
+                p_lo[h] = (int)rintf(__fmul_rn(__fsub_rn(w127, hf), 127.f));
+                m[h] = mnew;
+            }
+            const uint4 codes = make_uint4(pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), pack4(p_hi[4], p_hi[5], p_hi[6], p_hi[7]),
+                                           pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]), pack4(p_lo[4], p_lo[5], p_lo[6], p_lo[7]));
+            *reinterpret_cast<uint4 *>(sm.ptr + kSmP + buf * 2048u + tid * 16u) = codes;
+            if (DEBUG && rec < dbg.maxTiles)
+                reinterpret_cast<uint4 *>(dbg.pCodes)[(uint64_t)rec * 128u + tid] = codes;
+            fence_proxy_async_smem();
+            mbar_arrive(sm.bar(kBarPReady + buf));
+
+            if (have_prev && !drain(prev_gt, prev_kind, prev_rec)) return;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) r_prev[h] = r[h];
+            have_prev = true; prev_gt = gt; prev_kind = kind; prev_rec = rec;
+        }
+        if (have_prev && !drain(prev_gt, prev_kind, prev_rec)) return;
+
+        // ---------------- denominators: sum the per-thread partial sums
+        {
+            const float wsum = warp_sum8(l, lane);
+            float *slot_red = red;                      // buffer 0, after a sync of its own
+            if (!group_sync(sm, group_phase)) return;   // everyone is past the last tile's reads of `red`
+            if ((lane & 3u) == 0) slot_red[warp * 8u + reduced_value_index(lane)] = wsum;
+            if (!group_sync(sm, group_phase)) return;
+#pragma unroll
+            for (int h = 0; h < 8; ++h)
+                l[h] = __fadd_rn(__fadd_rn(slot_red[h], slot_red[8 + h]), __fadd_rn(slot_red[16 + h], slot_red[24 + h]));
+        }
+
+        __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.out) + (uint64_t)it.token * 4096u;
+        float *lse = p.lse ? reinterpret_cast<float *>(p.lse) + (uint64_t)it.token * 8u : nullptr;
+        if (it.nparts == 1) {
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb)
+                    out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], l[h]));
+            }
+            if (lse && tid < 8) {
+                float mm = m[0], ll = l[0];
+#pragma unroll
+                for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = m[h]; ll = l[h]; }
+                lse[tid] = __fadd_rn(mm, logf(ll));
+            }
+            continue;
+        }
+
+        // ---------------- piece of a token shared with other CTAs
+        const uint32_t my_slot = it.part == 0 ? it.first_cta * 2u + 1u : (it.first_cta + it.part) * 2u;
+        float *mine = partials + (uint64_t)my_slot * kPartialFloats;
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + tid] = acc[mb][h];
+        if (tid < 8) {
+            float mm = m[0], ll = l[0];
+#pragma unroll
+            for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = m[h]; ll = l[h]; }
+            mine[4096 + tid] = mm;
+            mine[4104 + tid] = ll;
+        }
+        __threadfence();
+        if (!group_sync(sm, group_phase)) return;
+        if (tid == 0) misc[2] = atomicAdd(tickets + it.token, 1u);
+        if (!group_sync(sm, group_phase)) return;
+        const uint32_t ticket = misc[2];
+        if (ticket + 1u != it.nparts) continue;
+        __threadfence();
+        float top[8], den[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
+        for (uint32_t j = 0; j < it.nparts; ++j) {
+            const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+            const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
+        }
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
+        for (uint32_t j = 0; j < it.nparts; ++j) {
+            const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+            const float *ps = partials + (uint64_t)sl * kPartialFloats;
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                const float g = expf(__fsub_rn(__ldcg(ps + 4096 + h), top[h]));
+                den[h] = __fadd_rn(den[h], __fmul_rn(__ldcg(ps + 4104 + h), g));
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb)
+                    acc[mb][h] = __fadd_rn(acc[mb][h], __fmul_rn(__ldcg(ps + h * 512 + mb * 128 + tid), g));
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb)
+                out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
+        if (lse && tid < 8) {
+            float mm = top[0], ll = den[0];
+#pragma unroll
+            for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = top[h]; ll = den[h]; }
+            lse[tid] = __fadd_rn(mm, logf(ll));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode kernel
+template <int RATIO, bool DEBUG>
+__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs p, const SharedKVDebug dbg)
+{
+    extern __shared__ char smem_raw[];
+    Shared sm;
+    {
+        const uint32_t raw = smem_addr(smem_raw);
+        const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+        sm.base = raw + pad;
+        sm.ptr = smem_raw + pad;
+    }
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    volatile uint32_t *misc = sm.misc();
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) { mbar_init(sm.bar(kBarFull + s), 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
+        for (uint32_t b = 0; b < 2; ++b) {
+            mbar_init(sm.bar(kBarSFull + b), 1); mbar_init(sm.bar(kBarSFree + b), 128);
+            mbar_init(sm.bar(kBarPReady + b), 128); mbar_init(sm.bar(kBarOFull + b), 1); mbar_init(sm.bar(kBarOFree + b), 128);
+        }
+        mbar_init(sm.bar(kBarQReady), 128);
+        mbar_init(sm.bar(kBarGroup), 128);
+        misc[1] = 0; misc[2] = 0;
+        fence_mbar_init();
+    }
+    if (warp == 8) {
+        tmem_alloc(sm.base + kSmMisc, kTmemCols);
+        tmem_relinquish();
+    }
+    {
+        float *scales = reinterpret_cast<float *>(sm.ptr + kSmScale);
+        const float *os = reinterpret_cast<const float *>(p.oriScale), *cs = reinterpret_cast<const float *>(p.cmpScale);
+        for (uint32_t i = tid; i < 512u; i += kThreads) { scales[i] = os[i]; scales[512 + i] = cs[i]; }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = misc[0];
+
+    const char *ws = reinterpret_cast<const char *>(p.workspace);
+    const PlanHeader *header = reinterpret_cast<const PlanHeader *>(ws);
+    const uint32_t *cta_first = reinterpret_cast<const uint32_t *>(ws + kWsCtaFirst);
+    const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
+    const uint32_t first = cta_first[blockIdx.x], end = cta_first[blockIdx.x + 1];
+
+    if (warp < 4) {
+        softmax_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
+    } else if (warp < 8) {
+        producer_loop<RATIO>(p, sm, items, first, end, warp - 4u, lane);
+        cp_async_wait<0>();
+    } else {
+        if (lane == 0) mma_loop(sm, items, first, end, tmem);
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && misc[1])
+        reinterpret_cast<PlanHeader *>(const_cast<char *>(ws))->status = kStatusWaitTimeout;
+    if (warp == 8) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+template <int RATIO>
+int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debug, int sms)
+{
+    uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
+    if (debug && debug->reserved && debug->reserved < grid) grid = debug->reserved;
+    plan_kernel<RATIO><<<1, kPlanThreads, 0, stream>>>(a, grid);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    SharedKVDebug d = {};
+    int device = 0;
+    e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    // the opt-in to > 48 KB of dynamic shared memory is per device and per kernel
+    static std::atomic<uint64_t> configured[2];
+    const uint64_t bit = 1ull << (device & 63);
+    if (debug) {
+        d = *debug;
+        if (!(configured[1].load(std::memory_order_relaxed) & bit)) {
+            e = cudaFuncSetAttribute(decode_kernel<RATIO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+            if (e != cudaSuccess) return (int)e;
+            configured[1].fetch_or(bit, std::memory_order_relaxed);
+        }
+        decode_kernel<RATIO, true><<<grid, kThreads, kSmemBytes, stream>>>(a, d);
+    } else {
+        if (!(configured[0].load(std::memory_order_relaxed) & bit)) {
+            e = cudaFuncSetAttribute(decode_kernel<RATIO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+            if (e != cudaSuccess) return (int)e;
+            configured[0].fetch_or(bit, std::memory_order_relaxed);
+        }
+        decode_kernel<RATIO, false><<<grid, kThreads, kSmemBytes, stream>>>(a, d);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+uint64_t workspace_bytes(uint32_t tokens)
+{
+    return ws_partials(tokens) + (uint64_t)kMaxCtas * 2ull * kPartialFloats * 4ull;
+}
+
+int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, const SharedKVDebug *debug)
+{
+    if (args == nullptr) return SHAREDKV_EINVAL;
+    if (variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
+        return SHAREDKV_EVARIANT;
+    const SharedKVArgs a = *args;
+    if (a.tokens == 0 || a.batch == 0) return SHAREDKV_OK;
+    const uint32_t ratio = variant == SHAREDKV_VARIANT_C128 ? 128u : 4u;
+    if (a.ratio != ratio || a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage || a.cmpBlock != kPage ||
+        a.oriIndices != 0)
+        return SHAREDKV_EINVAL;
+    if (ratio == 4 && (a.topk == 0 || a.topk > 1024u || !a.indices || a.indices % 4u)) return SHAREDKV_EINVAL;
+    if (!a.q || !a.ori || !a.cmp || !a.oriScale || !a.cmpScale || !a.oriTable || !a.cmpTable || !a.cuQ || !a.seqLens ||
+        !a.sinks || !a.out || !a.workspace)
+        return SHAREDKV_EINVAL;
+    // 16-byte row gathers and vector stores
+    if (a.q % 16u || a.out % 16u || a.ori % 16u || a.cmp % 16u || a.oriStride % 16u || a.cmpStride % 16u ||
+        a.workspace % 256u || a.oriScale % 4u || a.cmpScale % 4u || a.sinks % 4u || a.lse % 4u || a.oriTable % 4u ||
+        a.cmpTable % 4u || a.cuQ % 4u || a.seqLens % 4u)
+        return SHAREDKV_EINVAL;
+    if (a.oriStride < (uint64_t)kPage * kDim || a.cmpStride < (uint64_t)kPage * kDim) return SHAREDKV_EINVAL;
+    if (a.oriTableWidth == 0 || a.cmpTableWidth == 0 || a.oriPages == 0) return SHAREDKV_EINVAL;
+    if (debug && (!debug->tileInfo || !debug->validMask || !debug->qkAcc || !debug->pCodes || !debug->pvAcc ||
+                  !debug->qCodes || !debug->counter))
+        return SHAREDKV_EINVAL;
+    const int sms = device_sm_count();
+    if (sms <= 0) return (int)cudaErrorInvalidDevice;
+    return ratio == 4 ? launch<4>(a, stream, debug, sms) : launch<128>(a, stream, debug, sms);
+}
+
+}  // namespace sharedkv

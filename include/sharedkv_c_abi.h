@@ -1,0 +1,156 @@
+/*
+ * C ABI of libsharedkv_cuda.so: INT8 shared-KV decode attention and the paged
+ * INT8 KV-cache writer for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, symbol for symbol, what the reference project's Python
+ * layer binds for this path (paths below are relative to the reference checkout):
+ *
+ *   - the device libraries' C launchers
+ *       launch_sharedkv_c8_sparse        csrc/kernels/c8/c4.cpp:70
+ *       launch_sharedkv_c8_dense         csrc/kernels/c8/c128.cpp:107
+ *       launch_sharedkv_c8_sparse_small  csrc/kernels/c8/c4_small.cpp:21
+ *       launch_cache_write               csrc/kernels/cache_write.cpp:71
+ *     (ctypes signatures: npu_sparse_attn_sharedkv_int8/c8_attention.py:49-52,
+ *      npu_sparse_attn_sharedkv_int8/cache.py:48-50), and
+ *   - the pybind11 host bridge (csrc/host/launch.cpp:105-115,
+ *     csrc/host/c8_launch.cpp:38-43): attention / cache_write by argument
+ *     address, ABI-size attributes, variant count.
+ *
+ * Rules of the boundary
+ *   - plain C types only; every pointer field is a device address of the GPU
+ *     that is current (or named by `device`) when the call is made;
+ *   - the library allocates nothing, synchronises nothing and reads nothing
+ *     back: all scratch comes in through SharedKVArgs.workspace, whose size the
+ *     caller obtains from sharedkv_workspace_bytes();
+ *   - argument structs are copied by value at launch, so the caller may rebind
+ *     or free the host struct as soon as the call returns;
+ *   - launches go to the stream handed in (a cudaStream_t passed as void*) and
+ *     may be captured in a CUDA graph: live batch and token counts are derived
+ *     on the device from cuQ / seqLens on every replay;
+ *   - every entry returns 0 on success, a negative SHAREDKV_E* code for a
+ *     contract violation detected on the host, or a positive cudaError_t.
+ *     (The reference launchers return void; a caller that ignores the result
+ *     keeps working.)
+ */
+#ifndef SHAREDKV_C_ABI_H
+#define SHAREDKV_C_ABI_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SHAREDKV_API __attribute__((visibility("default")))
+#else
+#define SHAREDKV_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Byte-for-byte the reference's SharedKVArgs (csrc/kernels/c8/args.h:7-14,
+ * mirrored by ctypes in npu_sparse_attn_sharedkv_int8/attention.py:11-17): 200 bytes.
+ * Strides are in bytes between consecutive pages; block tables hold page ids. */
+typedef struct SharedKVArgs {
+    uint64_t q;          /* BF16 [tokens, heads, 512], contiguous                    */
+    uint64_t ori;        /* INT8 original cache  [oriPages, oriBlock, 1, 512]        */
+    uint64_t cmp;        /* INT8 compressed cache [*, cmpBlock, 1, 512]              */
+    uint64_t oriScale;   /* FP32 [512] frozen scale of the original cache            */
+    uint64_t cmpScale;   /* FP32 [512] frozen scale of the compressed cache          */
+    uint64_t oriTable;   /* INT32 [batch, oriTableWidth] logical page -> page id     */
+    uint64_t cmpTable;   /* INT32 [batch, cmpTableWidth]                             */
+    uint64_t indices;    /* INT32 [tokens, 1, topk] compressed rows (ratio 4 only)   */
+    uint64_t cuQ;        /* INT32 [batch + 1] cumulative query tokens                */
+    uint64_t seqLens;    /* INT32 [batch] KV length including the query tokens       */
+    uint64_t sinks;      /* FP32 [heads] sink logits                                 */
+    uint64_t out;        /* BF16 [tokens, heads, 512]                                */
+    uint64_t workspace;  /* >= sharedkv_workspace_bytes(tokens) bytes, 256-aligned   */
+    uint64_t lse;        /* FP32 [tokens, heads] or 0                                */
+    uint64_t oriStride;  /* bytes between original pages (>= oriBlock * 512)         */
+    uint64_t cmpStride;  /* bytes between compressed pages                           */
+    uint64_t partial;    /* unused by this library (kept for layout compatibility)   */
+    uint64_t oriIndices; /* must be 0: explicit original slots are not on this path  */
+    uint32_t tokens, heads, batch, oriBlock, cmpBlock, oriTableWidth, cmpTableWidth;
+    uint32_t ratio, window, topk, splits, oriTopk, oriPages;
+    float softmaxScale;
+} SharedKVArgs;
+
+/* Byte-for-byte the reference's CacheWriteArgs (csrc/kernels/cache_write.h:4-8,
+ * npu_sparse_attn_sharedkv_int8/cache.py:10-13): 84 bytes padded to 88.
+ * pageStride in bytes; updateStride, slotStride, slotColumnStride in elements. */
+typedef struct CacheWriteArgs {
+    uint64_t cache, updates, slots, inverseScale;
+    uint64_t pageStride, updateStride, slotStride, slotColumnStride;
+    uint32_t tokens, pages, pageSize, int64Slots, pairedSlots;
+} CacheWriteArgs;
+
+enum {
+    SHAREDKV_OK = 0,
+    SHAREDKV_EINVAL = -22,     /* null pointer, unsupported geometry, bad alignment  */
+    SHAREDKV_ERANGE = -34,     /* batch / tokens beyond what the workspace can plan   */
+    SHAREDKV_EVARIANT = -2     /* unknown kernel variant (launch.cpp:45 throws there) */
+};
+
+/* Kernel variants of the host bridge (c8_launch.cpp:12-18). */
+enum { SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
+
+/* sizeof(SharedKVArgs) / sizeof(CacheWriteArgs) as compiled into the library; the
+ * Python layer compares them with its ctypes mirrors (attention.py:223-226,
+ * cache.py:54-55; exported as module attributes by launch.cpp:112-114). */
+SHAREDKV_API uint32_t sharedkv_attention_args_size(void);
+SHAREDKV_API uint32_t sharedkv_cache_args_size(void);
+/* One past the largest accepted attention variant (launch.cpp:113). */
+SHAREDKV_API uint32_t sharedkv_attention_variant_count(void);
+
+/* Scratch the attention launch needs for `tokens` query rows, in bytes.
+ * Replaces the Python-side constant c8_attention.WORKSPACE_BYTES
+ * (npu_sparse_attn_sharedkv_int8/c8_attention.py:22-30). */
+SHAREDKV_API uint64_t sharedkv_workspace_bytes(uint32_t tokens);
+
+/* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
+ * query token.  `blocks` is accepted for signature compatibility and ignored: the
+ * grid is one persistent CTA per SM.  Replaces c4.cpp:70. */
+SHAREDKV_API int launch_sharedkv_c8_sparse(uint32_t blocks, void *stream, const SharedKVArgs *args);
+/* Same kernel; the reference kept a second image for capacities below 24 tokens
+ * (c4_small.cpp:21).  Kept as a distinct symbol because the Python layer selects it. */
+SHAREDKV_API int launch_sharedkv_c8_sparse_small(uint32_t blocks, void *stream, const SharedKVArgs *args);
+/* C128 (ratio 128): window + every compressed row of the context.  Replaces c128.cpp:107. */
+SHAREDKV_API int launch_sharedkv_c8_dense(uint32_t blocks, void *stream, const SharedKVArgs *args);
+
+/* Fused BF16 -> INT8 quantize (x * inverseScale, round-half-even, clamp +-127) and
+ * slot scatter.  Rows with a negative slot, page >= pages or offset outside
+ * [0, pageSize) are skipped.  Replaces cache_write.cpp:71. */
+SHAREDKV_API int launch_cache_write(uint32_t blocks, void *stream, const CacheWriteArgs *args);
+
+/* Host-bridge forms: `args` is the address of a host SharedKVArgs / CacheWriteArgs,
+ * `device` the CUDA ordinal to make current for the launch (restored before return).
+ * Replace attention()/cache_write() of csrc/host/c8_launch.cpp:20-25 and
+ * csrc/host/launch.cpp:27-54; the stream is explicit because this library does not
+ * link the tensor framework that owns the "current stream". */
+SHAREDKV_API int sharedkv_attention(uint64_t args, uint32_t blocks, uint32_t variant, int32_t device, void *stream);
+SHAREDKV_API int sharedkv_cache_write(uint64_t args, uint32_t blocks, int32_t device, void *stream);
+
+/* Test hook: as the attention launchers (variant selects the kernel), additionally
+ * dumping integer intermediates of every 128-key tile for exact comparison:
+ *   tileInfo  INT32 [maxTiles, 4]       {token, kind, tile-in-kind, 128-bit mask word 0..3 packed below}
+ *   validMask UINT32 [maxTiles, 4]      which of the tile's 128 slots are real keys
+ *   qkAcc     INT32 [maxTiles, 128, 16] QK accumulators (columns 0-7 hi plane, 8-15 lo plane)
+ *   pCodes    INT8  [maxTiles, 128, 16] P codes (0-7 hi, 8-15 lo)
+ *   pvAcc     INT32 [maxTiles, 512, 16] PV accumulators
+ *   qCodes    INT8  [tokens, 2, 16, 512] query code planes per cache kind
+ *   counter   UINT32 [1]                 tiles dumped (zeroed by the caller)
+ * No counterpart in the reference; its oracle computes these inline
+ * (npu_sparse_attn_sharedkv_int8/reference.py:287-289,310-313). */
+typedef struct SharedKVDebug {
+    uint64_t tileInfo, validMask, qkAcc, pCodes, pvAcc, qCodes, counter;
+    uint32_t maxTiles, reserved;
+} SharedKVDebug;
+SHAREDKV_API int sharedkv_attention_debug(uint32_t variant, void *stream, const SharedKVArgs *args,
+                             const SharedKVDebug *debug);
+
+/* Human-readable text for a value returned by any entry above. */
+SHAREDKV_API const char *sharedkv_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHAREDKV_C_ABI_H */

@@ -1,0 +1,180 @@
+"""Generate the golden vectors under tests/golden/ from the reference project itself.
+
+Run once, in a container that has the reference checkout (it is not needed to run the
+tests):
+
+    TORCH_DEVICE_BACKEND_AUTOLOAD=0 python tests/golden/make_golden.py --reference /path/to/reference
+
+Every array written here is an input to, or an output of, the reference's own Python
+functions: `CacheQuantization.quantize`, `tiled_quantized_reference`, `sharedkv_reference`
+and `joint_quantized_row` (npu_sparse_attn_sharedkv_int8/reference.py) and, for the
+"real" cases, `ActivationCorpus.make` (tests/support/serving_shapes.py) with the frozen
+scale file shipped in the reference package.  BF16 tensors are stored as their uint16 bit
+patterns.  The tests compare the oracle in oracle/ and the CUDA library against them.
+"""
+import argparse
+from dataclasses import replace
+import math
+from pathlib import Path
+import sys
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def save_case(name, case, oq, cq, ref, extra=None):
+    torch.set_num_threads(4)
+    arrays = dict(
+        q=bits(case.q), ori=case.ori.numpy(), ori_table=case.ori_block_table.numpy(),
+        cmp=case.cmp.numpy(), cmp_table=case.cmp_block_table.numpy(),
+        cu_q=case.cu_q.numpy(), seq_lens=case.seq_lens.numpy(), sink=case.sink.numpy(),
+        ori_scale=oq.scale.numpy(), cmp_scale=cq.scale.numpy(),
+        ratio=np.int32(case.ratio), softmax_scale=np.float64(case.softmax_scale))
+    if case.cmp_indices is not None:
+        arrays['cmp_indices'] = case.cmp_indices.numpy()
+    for splits in (1, 2, 3):
+        out, lse = ref.tiled_quantized_reference(case, oq, cq, tile_size=128, splits=splits, return_lse=True)
+        arrays[f'out_s{splits}'] = bits(out)
+        arrays[f'lse_s{splits}'] = lse.numpy()
+    decoded = replace(case, ori=oq.dequantize(case.ori), cmp=cq.dequantize(case.cmp))
+    out64, lse64 = ref.sharedkv_reference(decoded)
+    arrays['out_fp64'] = out64.numpy()
+    arrays['lse_fp64'] = lse64.numpy()
+    if extra:
+        arrays.update(extra)
+    np.savez_compressed(HERE / f'{name}.npz', **arrays)
+    print(name, {k: v.shape for k, v in arrays.items() if hasattr(v, 'shape') and v.ndim}, flush=True)
+
+
+def windowed_case(ref, *, ratio, queries, lengths, seed, topk=1024, edit_indices=None):
+    """Synthetic case of the BASELINE config family: lognormal per-channel spread, scale =
+    1.1 * absmax / 127, page tables that are random permutations of the page pool, and only
+    the window pages of the original cache allocated (as a sliding-window allocator does)."""
+    g = torch.Generator().manual_seed(seed)
+    batch, tokens = len(queries), sum(queries)
+    sigma = torch.exp(torch.randn(512, generator=g) * 0.5)
+
+    def pool(ranges, width):
+        count = max(1, sum(len(r) for r in ranges))
+        order = torch.randperm(count, generator=g, dtype=torch.int32)
+        table = torch.zeros((batch, width), dtype=torch.int32)
+        offset = 0
+        for b, r in enumerate(ranges):
+            if len(r):
+                table[b, list(r)] = order[offset:offset + len(r)]
+                offset += len(r)
+        rows = (torch.randn(count, 32, 1, 512, generator=g) * sigma).bfloat16()
+        return rows, table
+
+    ori_ranges = [range(max(0, s - q - 127) // 32, (s - 1) // 32 + 1) for q, s in zip(queries, lengths)]
+    ori, ori_table = pool(ori_ranges, math.ceil(max(lengths) / 32))
+    cmp_ranges = [range(math.ceil((s // ratio) / 32)) for s in lengths]
+    cmp, cmp_table = pool(cmp_ranges, max(1, math.ceil(max(lengths) / (ratio * 32))))
+    oq = ref.CacheQuantization((ori.float().reshape(-1, 512).abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
+    cq = ref.CacheQuantization((cmp.float().reshape(-1, 512).abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
+    indices = None
+    if ratio == 4:
+        indices = torch.full((tokens, 1, topk), -1, dtype=torch.int32)
+        t = 0
+        for q, s in zip(queries, lengths):
+            for local in range(q):
+                count = (s - q + local + 1) // 4
+                chosen = torch.randperm(count, generator=g, dtype=torch.int32)[:topk]
+                indices[t, 0, :len(chosen)] = chosen
+                t += 1
+        if edit_indices is not None:
+            edit_indices(indices, g)
+    cu = torch.tensor([0, *np.cumsum(queries).tolist()], dtype=torch.int32)
+    case = ref.SharedKVCase(q=torch.randn(tokens, 8, 512, generator=g).bfloat16(), ori=oq.quantize(ori),
+                            ori_block_table=ori_table, cu_q=cu, seq_lens=torch.tensor(lengths, dtype=torch.int32),
+                            sink=torch.linspace(-2, 2, 8), cmp=cq.quantize(cmp), cmp_block_table=cmp_table,
+                            cmp_indices=indices, ratio=ratio)
+    return case, oq, cq
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument('--reference', type=Path, default=Path('/root/reference'))
+    args = parser.parse_args()
+    sys.path.insert(0, str(args.reference))
+    from npu_sparse_attn_sharedkv_int8 import reference as ref
+    from tests.support.serving_shapes import ActivationCorpus, Geometry
+
+    # ---- writer: known answers and a random block (reference tests/unit/test_reference.py:22-27)
+    g = torch.Generator().manual_seed(3)
+    sigma = torch.exp(torch.randn(512, generator=g) * 0.5)
+    rows = (torch.randn(96, 512, generator=g) * sigma).bfloat16()
+    rows[0, :8] = torch.tensor([-200.0, -127.0, -1.5, -0.5, 0.5, 1.5, 127.0, 200.0]).bfloat16()
+    quant = ref.CacheQuantization((rows.float().abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
+    unit = ref.CacheQuantization(torch.ones(512))
+    kat = torch.zeros(1, 512)
+    kat[0, :8] = torch.tensor([-200.0, -127.0, -1.5, -0.5, 0.5, 1.5, 127.0, 200.0])
+    halves = (torch.arange(-300, 300).float() / 2).bfloat16().reshape(1, -1)      # every half-integer tie
+    halves = torch.nn.functional.pad(halves, (0, 1024 - halves.shape[1])).reshape(2, 512)
+    np.savez_compressed(HERE / 'writer.npz', rows=bits(rows), scale=quant.scale.numpy(),
+                        inverse_scale=quant.inverse_scale.numpy(), codes=quant.quantize(rows).numpy(),
+                        kat_rows=kat.numpy(), kat_codes=unit.quantize(kat).numpy(),
+                        tie_rows=bits(halves), tie_codes=unit.quantize(halves).numpy())
+
+    # ---- joint-softmax known answer (tests/unit/test_reference.py:50-56)
+    q = torch.zeros(2, 512)
+    caches = [torch.full((1, 512), v, dtype=torch.int8) for v in (10, 20)]
+    out, lse = ref.joint_quantized_row(q, caches, [unit, unit], torch.zeros(2), 1.0)
+    g = torch.Generator().manual_seed(5)
+    jq = torch.randn(8, 512, generator=g).bfloat16()
+    jc = [torch.randint(-127, 128, (n, 512), generator=g, dtype=torch.int8) for n in (100, 77)]
+    jout, jlse = ref.joint_quantized_row(jq, jc, [quant, quant], torch.linspace(-2, 2, 8), 512 ** -0.5)
+    np.savez_compressed(HERE / 'joint.npz', kat_out=bits(out), kat_lse=lse.numpy(), q=bits(jq), c0=jc[0].numpy(),
+                        c1=jc[1].numpy(), scale=quant.scale.numpy(), out=bits(jout), lse=jlse.numpy())
+
+    # ---- the reference's own unit-test geometry (tests/unit/test_reference.py:59-71)
+    for ratio in (4, 128):
+        case = ref.make_case(query_lengths=(2, 1), seq_lens=(129, 257), ratio=ratio, seed=23)
+        oq, cq = ref.CacheQuantization.calibrate([case.ori]), ref.CacheQuantization.calibrate([case.cmp])
+        save_case(f'unit_c{ratio}', replace(case, ori=oq.quantize(case.ori), cmp=cq.quantize(case.cmp)), oq, cq, ref)
+
+    # ---- BASELINE config 0: C4, B=2, T=1, contexts 4096 / 8192, top-k 1024, seed 0
+    case, oq, cq = windowed_case(ref, ratio=4, queries=[1, 1], lengths=[4096, 8192], seed=0)
+    save_case('config0_c4', case, oq, cq, ref)
+
+    # ---- C4 selections with holes, out-of-range entries and duplicates (count >= top-k: slots keep their place)
+    def damage(indices, g):
+        indices[:, :, ::7] = -1
+        indices[:, :, 5::11] = 2 ** 30
+        indices[:, :, 3::13] = indices[:, :, 2::13][:, :, :indices[:, :, 3::13].shape[-1]]
+        indices[1, :, 128:256] = -1                 # one tile with no key at all
+    case, oq, cq = windowed_case(ref, ratio=4, queries=[2, 1], lengths=[4300, 4100], seed=11, edit_indices=damage)
+    save_case('holes_c4', case, oq, cq, ref)
+
+    # ---- short contexts: fewer compressed rows than top-k slots (valid selections are packed), ragged queries,
+    #      a first token with no compressed row, duplicates among the packed entries
+    def shuffle_short(indices, g):
+        indices[0, 0, :] = indices[0, 0, torch.randperm(1024, generator=g)]
+        indices[2, 0, 100:140] = indices[2, 0, 0:40]
+    case, oq, cq = windowed_case(ref, ratio=4, queries=[1, 3, 1, 2], lengths=[700, 2051, 2, 131], seed=12,
+                                 edit_indices=shuffle_short)
+    save_case('short_c4', case, oq, cq, ref)
+
+    # ---- C128: contexts below one compressed row, one tile, several tiles; two query tokens in one request
+    case, oq, cq = windowed_case(ref, ratio=128, queries=[1, 2, 1, 1], lengths=[100, 16500, 40000, 129], seed=13)
+    save_case('mixed_c128', case, oq, cq, ref)
+
+    # ---- real activation rows with the frozen serving scales
+    corpus = ActivationCorpus()
+    for ratio, queries, lengths in ((4, (1, 2), (131, 1030)), (128, (2, 1), (4100, 9000))):
+        source, oq, cq, _ = corpus.make(Geometry(f'real_c{ratio}', ratio, queries, lengths), layer_index=0)
+        # keep only the table columns these lengths can touch
+        case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp),
+                       ori_block_table=source.ori_block_table[:, :math.ceil(max(lengths) / 32)].contiguous(),
+                       cmp_block_table=source.cmp_block_table[:, :max(1, math.ceil(max(lengths) / (ratio * 32)))].contiguous())
+        save_case(f'real_c{ratio}', case, oq, cq, ref)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,57 @@
+"""Helpers shared by the tests: golden cases as tensors, comparison metrics, device staging."""
+from dataclasses import replace
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, SharedKVCase
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+ATTENTION_CASES = ("unit_c4", "unit_c128", "config0_c4", "holes_c4", "short_c4", "mixed_c128", "real_c4", "real_c128")
+PAGE_STRIDE = 622592          # the non-unit page stride the reference's device tests use (tests/support/serving_shapes.py:19)
+
+
+def bf16(bits):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+
+def load_case(name):
+    """Returns (case, ori_scale, cmp_scale, arrays) for a golden attention case."""
+    z = np.load(GOLDEN / f"{name}.npz")
+    t = lambda key: torch.from_numpy(z[key].copy())
+    case = SharedKVCase(
+        q=bf16(z["q"]), ori=t("ori"), ori_block_table=t("ori_table"), cu_q=t("cu_q"), seq_lens=t("seq_lens"),
+        sink=t("sink"), cmp=t("cmp"), cmp_block_table=t("cmp_table"),
+        cmp_indices=t("cmp_indices") if "cmp_indices" in z else None,
+        ratio=int(z["ratio"]), softmax_scale=float(z["softmax_scale"]))
+    return case, t("ori_scale"), t("cmp_scale"), z
+
+
+def strided_pages(cache, device, stride=PAGE_STRIDE, offset=0):
+    """Copy cache[P,32,1,512] into a backing whose pages are `stride` bytes apart, starting
+    `offset` bytes in, and return the strided view (what a compact page allocator hands out)."""
+    pages = cache.shape[0]
+    raw = torch.zeros(pages * stride + offset, dtype=torch.int8, device=device)
+    view = raw[offset:].as_strided(cache.shape, (stride, 512, 512, 1))
+    view.copy_(cache.to(device))
+    return view
+
+
+def to_device(case, device, *, stride=None, offset=0):
+    dev = case.to(device)
+    if stride is not None:
+        dev = replace(dev, ori=strided_pages(case.ori, device, stride, offset),
+                      cmp=strided_pages(case.cmp, device, stride, offset))
+    return dev
+
+
+def error_metrics(actual, expected):
+    a, b = actual.double(), expected.double()
+    diff = (a - b).abs()
+    return dict(max_abs=float(diff.max()) if diff.numel() else 0.0, mean_abs=float(diff.mean()) if diff.numel() else 0.0,
+                rel_l2=float(torch.linalg.vector_norm(a - b) / torch.linalg.vector_norm(b).clamp_min(1e-30)))
+
+
+def synthetic_scale(rows):
+    return CacheQuantization((rows.float().reshape(-1, 512).abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
