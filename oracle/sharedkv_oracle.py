@@ -177,12 +177,17 @@ class Trace:
 
 
 def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
-                    return_lse=False, trace: Trace | None = None):
+                    return_lse=False, trace: Trace | None = None, tile_parts=None):
     """Online-softmax INT8 attention, tile by tile   (reference.py:210-323).
 
     Tiles are numbered original-first then compressed and dealt round-robin
     to `splits` partial states; every state starts at max = sink, and only
     state 0 starts with the sink's unit in its denominator.
+
+    `tile_parts` (token -> list of state numbers, one per tile) replaces the
+    round-robin deal by an explicit one, so that the oracle can follow a device
+    that cuts a token's tiles into contiguous pieces; tiles beyond the list go to
+    the last state named.  The merge formula is the same.
     """
     heads = case.q.shape[1]
     outputs, lses = [], []
@@ -192,6 +197,9 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
                    torch.ones_like(sel.ori_index, dtype=torch.bool), ori_scale)]
         if case.ratio != 1:
             groups.append((case.cmp, case.cmp_block_table, sel.cmp_index, sel.cmp_valid, cmp_scale))
+        deal = tile_parts[token] if tile_parts is not None else None
+        if deal is not None:
+            splits = max(deal) + 1
         maximum = case.sink.repeat(splits, 1)
         denominator = torch.zeros(splits, heads)
         denominator[0].fill_(1)
@@ -202,7 +210,7 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
             if trace is not None:
                 trace.q_codes[(token, kind)] = (alpha, q_hi, q_lo)
             for start in range(0, index.numel(), tile_size):
-                part = tile_number % splits
+                part = tile_number % splits if deal is None else deal[min(tile_number, len(deal) - 1)]
                 tile_number += 1
                 ix, keep = index[start:start + tile_size], valid[start:start + tile_size]
                 kv = torch.zeros((ix.numel(), DIM), dtype=torch.int32)

@@ -55,3 +55,27 @@ def error_metrics(actual, expected):
 
 def synthetic_scale(rows):
     return CacheQuantization((rows.float().reshape(-1, 512).abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
+
+
+def device_tile_parts(case, ctas):
+    """Which piece each 128-key tile of each token belongs to when the flat tile list of a
+    launch is cut into `ctas` equal contiguous ranges (the CUDA plan kernel's rule): a C4
+    token with at least one compressed row has 1 + ceil(topk / 128) tiles, a C128 token
+    1 + ceil(rows / 128), a token that sees no compressed row has 1."""
+    counts = []
+    for batch in range(case.seq_lens.numel()):
+        first, last = int(case.cu_q[batch]), int(case.cu_q[batch + 1])
+        for token in range(first, last):
+            position = int(case.seq_lens[batch]) - last + token
+            rows = (position + 1) // case.ratio if position >= 0 else 0
+            if case.ratio == 4:
+                counts.append(1 + (-(-case.cmp_indices.shape[-1] // 128) if rows else 0))
+            else:
+                counts.append(1 + -(-rows // 128))
+    total = sum(counts)
+    quota = max(1, -(-total // ctas))
+    parts, start = {}, 0
+    for token, n in enumerate(counts):
+        parts[token] = [(start + j) // quota - start // quota for j in range(n)]
+        start += n
+    return parts
