@@ -1,0 +1,414 @@
+"""Benchmark of the INT8 shared-KV decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload box|c128|c4mtp]
+
+Default workload ("box"): the box-scale decode step.  2048 concurrent requests with context
+lengths log-uniform over 4k..1M tokens are batch-sharded over the N GPUs (longest-first
+greedy by KV rows); every GPU holds the INT8 paged KV of its requests for alternating
+C4 (top-k 1024 + window 128) and C128 (all compressed rows + window 128) layers, as many
+layer pairs as fill about --kv-gb of its HBM.  A step is one decode pass of the hot path
+over all resident layers: one attention launch per layer, T = 1 query token per request.
+There is no collective on the path; ranks only meet at the timing barriers.
+
+Printed JSON line (rank 0): `value` = (request, layer) attention evaluations per second
+over all GPUs with everything resident in HBM; `e2e` = the same through the prepared
+operators with host buffers: per step and layer the new KV row of every request, Q and
+(C4) the top-k selections are copied from pinned host memory, the cache writer and the
+attention run, and the BF16 output is copied back.  `roofline` is for the dominant kernel
+(the C4 decode launch): algorithmic KV bytes per launch over its mean CUDA-event duration.
+`--impl reference` times the CPU restatement of the reference's Python path (the reference
+itself is Python and does not travel to the GPU box) on a bounded seeded sample.
+"""
+import argparse
+import json
+import math
+import os
+from pathlib import Path
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = Path(__file__).resolve().parent
+for entry in (ROOT / "ascend-int8-attention_b200", ROOT):
+    if str(entry) not in sys.path:
+        sys.path.insert(0, str(entry))
+
+import torch  # noqa: E402
+
+METRIC = "decode attn queries/s/GPU & achieved HBM GB/s (INT8 KV) at 1/2/4/8 B200"
+ROW_BYTES = 512
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- workloads
+def box_lengths(requests, seed=0):
+    from npu_sparse_attn_sharedkv_int8.synthetic import log_uniform_lengths
+    return log_uniform_lengths(requests, 4096, 1 << 20, seed)
+
+
+def shard(lengths, ranks):
+    """Longest-first greedy assignment of requests to ranks by KV rows per layer pair."""
+    cost = lengths // 4 + lengths // 128 + 256
+    order = torch.argsort(cost, descending=True).tolist()
+    load, owner = [0] * ranks, [[] for _ in range(ranks)]
+    for index in order:
+        r = min(range(ranks), key=load.__getitem__)
+        owner[r].append(index)
+        load[r] += int(cost[index])
+    return [sorted(o) for o in owner]
+
+
+def pair_bytes(lengths):
+    """Resident bytes of one C4 + C128 layer pair (compressed pools dominate)."""
+    c4 = ((lengths // 4 + 31) // 32).clamp_min(1).sum() * 16384
+    c128 = ((lengths // 128 + 31) // 32).clamp_min(1).sum() * 16384
+    ori = 2 * 6 * lengths.numel() * 16384
+    return int(c4 + c128 + ori)
+
+
+def build_workload(args, rank, world):
+    from npu_sparse_attn_sharedkv_int8 import synthetic
+    device = torch.device("cuda", torch.cuda.current_device())
+    if args.workload == "box":
+        lengths = box_lengths(args.requests, seed=0)
+        mine = lengths[torch.tensor(shard(lengths, world)[rank])]
+        per_pair = pair_bytes(mine)
+        pairs = max(1, round(args.kv_gb * 1e9 / per_pair))
+        while pairs > 1 and pairs * per_pair > 165e9:      # leave room for tables, queries and the context
+            pairs -= 1
+        if args.max_pairs:
+            pairs = min(pairs, args.max_pairs)
+        ratios = [4, 128] * pairs
+        work = synthetic.build("box", device, mine, ratios=ratios, queries=1, seed=100 + rank, max_context=1 << 20)
+        label = f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128"
+    elif args.workload == "c128":
+        lengths = synthetic.uniform_lengths(64, 8192, 131072, seed=1)
+        ratios = [128] * args.rotate
+        work = synthetic.build("c128", device, lengths, ratios=ratios, queries=1, seed=200 + rank, stride_slots=38,
+                               slot_offset=1, max_context=135000)
+        label = "C128 decode, B=64, T=1, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)"
+    else:
+        lengths = synthetic.uniform_lengths(256, 32768, 131072, seed=2)
+        ratios = [4] * args.rotate
+        work = synthetic.build("c4mtp", device, lengths, ratios=ratios, queries=2, seed=300 + rank, max_context=135000)
+        label = "C4 decode with MTP, B=256, T=2, ctx U[32k,128k], top-k 1024 + window 128"
+    return work, label
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, top, reasons = [], 0, set()
+        for line in text.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6 or not parts[0].isdigit():
+                continue
+            sm.append(int(parts[0]))
+            top = max(top, int(parts[1]))
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:]):
+                if value == "Active":
+                    reasons.add(name)
+        if not sm:
+            return None
+        busy = [v for v in sm if v >= 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": top, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU path (oracle port of the reference)
+def cpu_sample_case(ratio, lengths, seed):
+    """Small CPU case with the shapes of the workload's requests: every request carries the
+    rows it attends to (C4: 1024 selected rows + window; C128: all compressed rows + window)."""
+    from npu_sparse_attn_sharedkv_int8.reference import SharedKVCase
+    g = torch.Generator().manual_seed(seed)
+    batch = len(lengths)
+    new_lengths, ori_pages, cmp_pages = [], [], []
+    for length in lengths:
+        new_lengths.append(4097 if ratio == 4 else int(length))
+        cmp_pages.append(32 if ratio == 4 else max(1, math.ceil(int(length) // 128 / 32)))
+    ori_width = math.ceil(max(new_lengths) / 32)
+    ori_table = torch.zeros((batch, ori_width), dtype=torch.int32)
+    cmp_table = torch.zeros((batch, max(cmp_pages)), dtype=torch.int32)
+    used_ori = used_cmp = 0
+    for b, length in enumerate(new_lengths):
+        for page in range(max(0, length - 128) // 32, (length - 1) // 32 + 1):
+            ori_table[b, page] = used_ori
+            used_ori += 1
+        cmp_table[b, :cmp_pages[b]] = torch.arange(used_cmp, used_cmp + cmp_pages[b], dtype=torch.int32)
+        used_cmp += cmp_pages[b]
+    indices = None
+    if ratio == 4:
+        indices = torch.stack([torch.randperm(1024, generator=g).to(torch.int32) for _ in range(batch)]).view(batch, 1, 1024)
+    return SharedKVCase(
+        q=torch.randn(batch, 8, 512, generator=g).bfloat16(),
+        ori=torch.randint(-127, 128, (used_ori, 32, 1, 512), generator=g, dtype=torch.int8), ori_block_table=ori_table,
+        cu_q=torch.arange(batch + 1, dtype=torch.int32), seq_lens=torch.tensor(new_lengths, dtype=torch.int32),
+        sink=torch.linspace(-2, 2, 8), cmp=torch.randint(-127, 128, (used_cmp, 32, 1, 512), generator=g, dtype=torch.int8),
+        cmp_block_table=cmp_table, cmp_indices=indices, ratio=ratio)
+
+
+def time_cpu_path(lengths, ratios, budget_s, threads):
+    """Runs the CPU restatement of the reference path on batches of 8 requests per layer kind
+    until about `budget_s` seconds are spent.  Returns (queries/s, rows/s, queries timed)."""
+    from oracle import sharedkv_oracle as oracle
+    torch.set_num_threads(threads)
+    scale = torch.full((512,), 0.02)
+    g = torch.Generator().manual_seed(7)
+    kinds = sorted(set(ratios))
+    done, rows, spent = 0, 0, 0.0
+    oracle.attention_tiled(cpu_sample_case(kinds[0], [4096] * 2, 1), scale, scale)     # warm the thread pool
+    while spent < budget_s:
+        for ratio in kinds:
+            pick = lengths[torch.randint(len(lengths), (8,), generator=g)].tolist()
+            case = cpu_sample_case(ratio, pick, seed=done)
+            start = time.perf_counter()
+            oracle.attention_tiled(case, scale, scale)
+            spent += time.perf_counter() - start
+            done += len(pick)
+            rows += oracle.kv_rows_attended(case)
+    return done / spent, rows / spent, done
+
+
+# --------------------------------------------------------------------------- main
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    lengths = box_lengths(args.requests) if args.workload == "box" else None
+    if args.workload == "c128":
+        from npu_sparse_attn_sharedkv_int8.synthetic import uniform_lengths
+        lengths, ratios = uniform_lengths(64, 8192, 131072, seed=1), [128]
+    elif args.workload == "c4mtp":
+        from npu_sparse_attn_sharedkv_int8.synthetic import uniform_lengths
+        lengths, ratios = uniform_lengths(256, 32768, 131072, seed=2), [4]
+    else:
+        ratios = [4, 128]
+    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        time_cpu_path(lengths, ratios, per_step / 4, threads)
+    rates, row_rates, counted = [], [], 0
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        qps, rps, n = time_cpu_path(lengths, ratios, per_step, threads)
+        rates.append(qps); row_rates.append(rps); counted += n
+    elapsed = time.perf_counter() - start
+    value = statistics.mean(rates)
+    sample = f"{counted} queries in {args.steps} steps, batches of 8 requests per layer kind drawn from the workload's length distribution"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * elapsed / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": args.workload, "requests": args.requests},
+        "kv_gbs": statistics.mean(row_rates) * ROW_BYTES / 1e9,
+        "cpu_baseline": {"value": value, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    parser.add_argument("--workload", default="box", choices=("box", "c128", "c4mtp"))
+    parser.add_argument("--requests", type=int, default=2048)
+    parser.add_argument("--kv-gb", type=float, default=150.0)
+    parser.add_argument("--max-pairs", type=int, default=0)
+    parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
+    parser.add_argument("--cpu-seconds", type=float, default=12.0)
+    parser.add_argument("--no-e2e", action="store_true")
+    args = parser.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch.distributed as dist
+    from npu_sparse_attn_sharedkv_int8 import PreparedAttention, PreparedCacheWrite
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    work, label = build_workload(args, rank, world)
+    layers = len(work.layers)
+    ops = [PreparedAttention(work.case(i), work.layers[i].ori_scale, work.layers[i].cmp_scale) for i in range(layers)]
+    rows_per_layer = [work.kv_rows(i) for i in range(layers)]
+    queries_per_step = work.tokens * layers if args.workload == "box" else work.tokens
+    sequence = list(range(layers)) if args.workload == "box" else None
+
+    def step(index):
+        if sequence is not None:
+            for i in sequence:
+                ops[i].run()
+        else:
+            ops[index % layers].run()
+
+    # ---- resident-in-HBM timing, with per-layer events for the roofline
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    marks = []
+    begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for i in range(args.steps):
+        which = sequence if sequence is not None else [i % layers]
+        for layer in which:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); ops[layer].run(); b.record()
+            marks.append((layer, a, b))
+    finish.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = begin.elapsed_time(finish)
+    per_kind = {}
+    for layer, a, b in marks:
+        ratio = work.layers[layer].ratio
+        entry = per_kind.setdefault(ratio, [0.0, 0, 0])
+        entry[0] += a.elapsed_time(b); entry[1] += 1; entry[2] += rows_per_layer[layer]
+    times = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+    counts = torch.tensor([queries_per_step * args.steps, sum(rows_per_layer[l] for l, _, _ in marks)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+    total_ms = float(times[0])
+    value = float(counts[0]) / (total_ms / 1000)
+    kv_gbs = float(counts[1]) * ROW_BYTES / 1e9 / (total_ms / 1000)
+
+    # ---- end to end through the prepared operators with host buffers
+    e2e = None
+    if not args.no_e2e:
+        tokens = work.tokens
+        host_q = [torch.randn(tokens, 8, 512).bfloat16().pin_memory() for _ in range(min(layers, 4))]
+        host_rows = torch.randn(tokens, 512).bfloat16().pin_memory()
+        host_out = [torch.empty(tokens, 8, 512, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        host_idx = None
+        dev_rows = torch.empty(tokens, 512, dtype=torch.bfloat16, device=device)
+        # the new token of request b lands in the last row of its window: logical row seq_len - 1
+        last = (work.seq_lens_host - 1)
+        slot_pages = work.ori_table[torch.arange(work.requests, device=device), (last // 32).to(device)].long()
+        slots = (slot_pages * 32 + (last % 32).to(device)).to(torch.int32).repeat_interleave(work.queries)
+        writers, h2d, d2h = [], 0, 0
+        for i in range(layers):
+            layer = work.layers[i]
+            inverse = layer.ori_scale.double().reciprocal().float()
+            writers.append(PreparedCacheWrite(layer.ori, dev_rows, slots, inverse))
+            if layer.cmp_indices is not None and host_idx is None:
+                host_idx = layer.cmp_indices.cpu().pin_memory()
+        copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        main_stream = torch.cuda.current_stream(device)
+
+        def e2e_layer(i, slot):
+            nonlocal h2d, d2h
+            layer = work.layers[i]
+            layer.q.copy_(host_q[i % len(host_q)], non_blocking=True)
+            dev_rows.copy_(host_rows, non_blocking=True)
+            moved = layer.q.numel() * 2 + dev_rows.numel() * 2
+            if layer.cmp_indices is not None:
+                layer.cmp_indices.copy_(host_idx, non_blocking=True)
+                moved += host_idx.numel() * 4
+            writers[i].run()
+            out = ops[i].run()
+            host_out[slot].copy_(out, non_blocking=True)
+            h2d += moved
+            d2h += out.numel() * 2
+
+        def e2e_step(index):
+            which = sequence if sequence is not None else [index % layers]
+            for n, i in enumerate(which):
+                e2e_layer(i, n & 1)
+            torch.cuda.current_stream(device).synchronize()
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        h2d = d2h = 0
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        wall = time.perf_counter()
+        t0.record()
+        for i in range(args.steps):
+            e2e_step(i)
+        t1.record()
+        barrier()
+        wall = time.perf_counter() - wall
+        e2e_ms = torch.tensor([max(t0.elapsed_time(t1), 0.0)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        e2e = {"value": float(counts[0]) / (float(e2e_ms[0]) / 1000), "unit": "queries/s",
+               "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
+               "ms_per_step": float(e2e_ms[0]) / args.steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peaks()
+    roof = {}
+    for ratio, (ms, launches, rows) in per_kind.items():
+        achieved = rows * ROW_BYTES / 1e9 / (ms / 1000)
+        roof[ratio] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                       "traffic": None, "peak_source": peak_kind, "ms_per_launch": ms / launches,
+                       "algorithmic_bytes_per_launch": rows * ROW_BYTES // launches, "launches": launches}
+    dominant = max(per_kind, key=lambda r: per_kind[r][0])
+    cpu_qps, cpu_rows, cpu_n = time_cpu_path(work.seq_lens_host, [l.ratio for l in work.layers], args.cpu_seconds,
+                                             os.cpu_count() or 1)
+    line = {
+        "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": label, "requests": args.requests if args.workload == "box" else work.requests,
+                   "requests_on_rank0": work.requests, "layers_per_gpu": layers, "queries_per_step_rank0": queries_per_step,
+                   "kv_resident_gb_rank0": work.kv_bytes_resident / 1e9, "l2": "inputs larger than L2 (KV touched per step >> 126 MB)"
+                   if args.workload != "c128" else f"rotating {layers} cache copies, each launch reads a region not touched for {layers - 1} launches"},
+        "per_gpu_value": value / world, "kv_gbs": kv_gbs, "kv_gbs_per_gpu": kv_gbs / world,
+        "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}> (+ its plan kernel)"),
+        "roofline_other": {f"decode_kernel<{r}>": v for r, v in roof.items() if r != dominant},
+        "cpu_baseline": {"value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": "port",
+                         "sample": f"{cpu_n} queries, batches of 8 requests per layer kind drawn from rank 0's requests",
+                         "kv_gbs": cpu_rows * ROW_BYTES / 1e9},
+        "e2e": e2e, "gpu_launches": 2 * len(marks), "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
