@@ -34,11 +34,13 @@
 //   acc = acc r + (float(O_hi) + float(O_lo) * (1/127)) * scale_kind * (1/127)
 //   state starts at m = sink, l = 1 (first piece) or 0;  out = bf16(sum g acc / sum g l), g = exp(m - max m)
 // Every FP32 operation is a separately rounded IEEE operation (no FMA contraction).
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include <atomic>
+#include <cstring>
 
 #include "../../include/sharedkv_c_abi.h"
 #include "ptx_sm100.cuh"
@@ -55,7 +57,7 @@ constexpr uint32_t kTileKeys = 128;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
-constexpr uint32_t kThreads = 288;
+constexpr uint32_t kThreads = 416;                        // 4 softmax + 4 accumulate + 4 producer + 1 MMA warps
 constexpr uint32_t kMaxCtas = 160;
 constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
@@ -71,11 +73,15 @@ constexpr uint32_t kSmScale = kSmP + 2 * 2048;               // FP32 [2][512]
 constexpr uint32_t kSmMask = kSmScale + 2 * 2048;            // UINT32 [stages][4]
 constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2][4 warps][8]
 constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [2 kinds][8]: alpha * softmax_scale
-constexpr uint32_t kSmBar = kSmAlpha + 64;                   // mbarriers
+constexpr uint32_t kSmRescale = kSmAlpha + 64;               // [8 tiles][16]: r[8], debug record, pad
+constexpr uint32_t kSmFinal = kSmRescale + 8 * 64;           // [8 items][16]: m[8], l[8]
+constexpr uint32_t kSmBar = kSmFinal + 8 * 64;               // mbarriers
 constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kBarPReady = 10, kBarOFull = 12,
-                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17, kNumBars = 18;
-constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, ticket broadcast
+                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17 /* +1 for the accumulate warps */,
+                   kBarRescale = 19 /* x8 */, kBarItemDone = 27 /* x8 */, kNumBars = 35;
+constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words
 constexpr uint32_t kSmemBytes = kSmMisc + 16 + 1024;         // + alignment slack
+static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
 
 // tensor-memory columns
 constexpr uint32_t kTmemCols = 256;
@@ -143,13 +149,27 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
 }
 
 // ------------------------------------------------------------------ plan kernel
+constexpr uint32_t kPlanStaged = 11776;      // cuQ entries kept in shared memory (46 KB)
+
+// Request that owns query token t: the b with cu[b] <= t < cu[b + 1], 0 <= b < live_batch.
+__device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_batch, uint32_t t)
+{
+    uint32_t lo = 0, hi = live_batch - 1;
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (cu[mid + 1] <= (int32_t)t) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+
 template <int RATIO>
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p, const uint32_t grid)
 {
     __shared__ uint32_t scratch[80];
-    __shared__ uint32_t s_live;
+    __shared__ uint32_t s_live, s_mismatch;
+    __shared__ int32_t s_cu[kPlanStaged];
     const uint32_t tid = threadIdx.x;
-    const int32_t *cu = reinterpret_cast<const int32_t *>(p.cuQ);
+    const int32_t *cu_global = reinterpret_cast<const int32_t *>(p.cuQ);
     const int32_t *seq = reinterpret_cast<const int32_t *>(p.seqLens);
     char *ws = reinterpret_cast<char *>(p.workspace);
     PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
@@ -158,16 +178,25 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p
     uint32_t *tile_start = reinterpret_cast<uint32_t *>(ws + ws_tile_start(p.tokens));
     uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
 
-    if (tid == 0) s_live = 0;
+    if (tid == 0) { s_live = 0; s_mismatch = 0xffffffffu; }
+    const bool staged = p.batch + 1u <= kPlanStaged;
+    if (staged)
+        for (uint32_t b = tid; b <= p.batch; b += kPlanThreads) s_cu[b] = cu_global[b];
     __syncthreads();
-    uint32_t live = 0;
-    for (uint32_t b = tid; b < p.batch; b += kPlanThreads)
+    const int32_t *cu = staged ? s_cu : cu_global;
+    uint32_t live = 0, mismatch = 0xffffffffu;
+    for (uint32_t b = tid; b < p.batch; b += kPlanThreads) {
         if (seq[b] > 0 && cu[b + 1] >= 0) live = b + 1;
+        if (cu[b + 1] != (int32_t)(b + 1) && mismatch == 0xffffffffu) mismatch = b;
+    }
     if (live) atomicMax(&s_live, live);
+    if (mismatch != 0xffffffffu) atomicMin(&s_mismatch, mismatch);
     __syncthreads();
     const uint32_t live_batch = s_live;
     int32_t end = live_batch ? cu[live_batch] : 0;
     const uint32_t live_tokens = end <= 0 ? 0u : ((uint32_t)end < p.tokens ? (uint32_t)end : p.tokens);
+    // one query token per request (plain decode): token t belongs to request t
+    const bool one_each = live_tokens == live_batch && cu[0] == 0 && s_mismatch >= live_batch;
 
     // pass 1: flat tile offset of every live token
     uint32_t carry = 0;
@@ -175,12 +204,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p
         const uint32_t t = base + tid;
         uint32_t n = 0;
         if (t < live_tokens) {
-            uint32_t lo = 0, hi = live_batch - 1;
-            while (lo < hi) {
-                const uint32_t mid = (lo + hi) >> 1;
-                if (cu[mid + 1] <= (int32_t)t) lo = mid + 1; else hi = mid;
-            }
-            const int32_t position = seq[lo] - (cu[lo + 1] - (int32_t)t);
+            const uint32_t b = one_each ? t : owner_of(cu, live_batch, t);
+            const int32_t position = seq[b] - (cu[b + 1] - (int32_t)t);
             n = tiles_of_token(RATIO, position, p.topk);
         }
         uint32_t total;
@@ -200,13 +225,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p
         uint32_t pieces = 0, start = 0, n = 0, batch = 0;
         int32_t position = 0;
         if (t < live_tokens) {
-            uint32_t lo = 0, hi = live_batch - 1;
-            while (lo < hi) {
-                const uint32_t mid = (lo + hi) >> 1;
-                if (cu[mid + 1] <= (int32_t)t) lo = mid + 1; else hi = mid;
-            }
-            batch = lo;
-            position = seq[lo] - (cu[lo + 1] - (int32_t)t);
+            batch = one_each ? t : owner_of(cu, live_batch, t);
+            position = seq[batch] - (cu[batch + 1] - (int32_t)t);
             n = tiles_of_token(RATIO, position, p.topk);
             start = tile_start[t];
             pieces = (start + n - 1) / quota - start / quota + 1;
@@ -220,11 +240,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p
                 const uint32_t c = c0 + j;
                 const uint32_t lo_flat = max(start, c * quota), hi_flat = min(start + n, (c + 1) * quota);
                 const uint32_t index = item_carry + offset + j;
-                Item it;
-                it.token = t; it.batch = batch; it.position = position;
-                it.tile_begin = lo_flat - start; it.tile_end = hi_flat - start;
-                it.part = j; it.nparts = pieces; it.first_cta = c0;
-                items[index] = it;
+                uint4 *dst = reinterpret_cast<uint4 *>(items + index);
+                dst[0] = make_uint4(t, batch, (uint32_t)position, lo_flat - start);
+                dst[1] = make_uint4(hi_flat - start, j, pieces, c0);
                 if (lo_flat == c * quota) cta_first[c] = index;
             }
         }
@@ -248,10 +266,24 @@ struct Shared {
     __device__ __forceinline__ volatile uint32_t *misc() const { return reinterpret_cast<volatile uint32_t *>(ptr + kSmMisc); }
 };
 
+#ifdef SHAREDKV_TIMING
+// Development aid (not built by default): cycles spent waiting, per CTA, per role and barrier.
+__device__ unsigned long long g_wait_cycles[kMaxCtas][160];
+__device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
+{
+    const uint32_t warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31u) == 0 && (warp & 3u) == 0)
+        g_wait_cycles[blockIdx.x][(warp >> 2) * 40u + slot] += (unsigned long long)cycles;
+}
+#endif
+
 // Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.
 __device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
 {
     const uint32_t bar = sm.bar(bar_index);
+#ifdef SHAREDKV_TIMING
+    struct Scope { uint32_t i; long long t0; __device__ ~Scope() { timing_add(i, clock64() - t0); } } scope{bar_index, clock64()};
+#endif
     if (mbar_try_wait(bar, parity)) return true;
     volatile uint32_t *misc = sm.misc();
     const long long start = clock64();
@@ -339,28 +371,58 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
 }
 
-// ------------------------------------------------------------------ producer
-// Walks the CTA's tiles in order.  One cursor per pipeline stage of the producer.
+// ------------------------------------------------------------------ work-item cursors
+// Walks the CTA's tiles in order, keeping the next item's descriptor in flight so that moving
+// on to it does not expose a global-memory round trip.
 struct Cursor {
     uint32_t item, items_end, j;
     Item it;
+    uint4 next_lo, next_hi;
     bool done;
 };
+__device__ __forceinline__ Item decode_item(const uint4 &a, const uint4 &b)
+{
+    Item it;
+    it.token = a.x; it.batch = a.y; it.position = (int32_t)a.z; it.tile_begin = a.w;
+    it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
+    return it;
+}
+__device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items)
+{
+    if (c.item + 1 < c.items_end) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(items + c.item + 1);
+        c.next_lo = src[0];
+        c.next_hi = src[1];
+    }
+}
 __device__ __forceinline__ void cursor_init(Cursor &c, const Item *items, uint32_t first, uint32_t end)
 {
-    c.item = first; c.items_end = end; c.done = first >= end;
-    if (!c.done) { c.it = load_item(items, first); c.j = c.it.tile_begin; }
+    c.item = first; c.items_end = end; c.done = first >= end; c.j = 0;
+    c.next_lo = c.next_hi = make_uint4(0, 0, 0, 0);
+    if (!c.done) {
+        c.it = load_item(items, first);
+        c.j = c.it.tile_begin;
+        cursor_prefetch(c, items);
+    }
 }
 // Returns true when the cursor moved on to a new item.
 __device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items)
 {
     if (++c.j < c.it.tile_end) return false;
     if (++c.item >= c.items_end) { c.done = true; return false; }
-    c.it = load_item(items, c.item);
+    c.it = decode_item(c.next_lo, c.next_hi);
     c.j = c.it.tile_begin;
+    cursor_prefetch(c, items);
     return true;
 }
+// Skip whatever is left of the current item.
+__device__ __forceinline__ void cursor_next_item(Cursor &c, const Item *items)
+{
+    c.j = c.it.tile_end - 1u;
+    cursor_advance(c, items);
+}
 
+// ------------------------------------------------------------------ producer
 // Short-context C4 (fewer compressed rows than top-k slots): the valid selections are packed
 // to the front, order kept (reference.py:253).  Lane c keeps the validity mask of slots
 // [32 c, 32 c + 32) and the inclusive count up to and including its chunk.
@@ -405,10 +467,11 @@ __device__ __forceinline__ uint32_t compaction_slot(const Compaction &k, uint32_
     return chunk * 32u + (bit & 31u);
 }
 
-// Stage A of the producer: logical row of this lane's slot in the cursor's tile (may read the
-// top-k index array).  Returns -1 for a slot that holds no key.
+// Stage A of the producer: candidate logical row of this lane's slot in the cursor's tile.
+// Values read from the top-k array are returned unchecked (stage B range-checks them, so
+// that the load is not consumed here); every other path returns a valid row or -1.
 template <int RATIO>
-__device__ __forceinline__ int32_t logical_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot)
+__device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot)
 {
     const Item &it = c.it;
     if (it.position < 0) return -1;
@@ -417,22 +480,29 @@ __device__ __forceinline__ int32_t logical_row(const SharedKVArgs &p, const Curs
         return slot < n ? (int32_t)((uint32_t)it.position + 1u - n + slot) : -1;
     }
     const uint32_t s = (c.j - 1u) * kTileKeys + slot;
-    const uint32_t count = (uint32_t)(it.position + 1) / (uint32_t)RATIO;
-    if (RATIO == 128) return s < count ? (int32_t)s : -1;
+    if (RATIO == 128) return s < (uint32_t)(it.position + 1) / 128u ? (int32_t)s : -1;
     const int32_t *ix = reinterpret_cast<const int32_t *>(p.indices) + (uint64_t)it.token * p.topk;
     if (k.active) {
         const bool in_range = s < k.total;
         const uint32_t src = compaction_slot(k, s, in_range);
         return in_range ? ix[src] : -1;
     }
-    if (s >= p.topk) return -1;
-    const int32_t v = ix[s];
-    return (v >= 0 && (uint32_t)v < count) ? v : -1;
+    return s < p.topk ? ix[s] : -1;
 }
 
-template <int RATIO>
+// Producer warps.  Three stages, each `kLookahead` tiles behind the previous one, so that the
+// two dependent global reads in front of a row copy (top-k entry -> page-table entry -> row)
+// are issued several tiles before their results are needed:
+//   A  candidate logical row of this lane's slot          (tile n)
+//   B  range check + page-table lookup                    (tile n - kLookahead)
+//   C  16-byte cp.async copies of the 128 rows of a tile  (tile n - 2 kLookahead)
+constexpr int kLookahead = 4;
+
+constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
+
+template <int RATIO, bool TMA>
 __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, uint32_t first, uint32_t end,
-                              uint32_t pw, uint32_t lane)
+                              uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map)
 {
     Cursor ca, cb, cc;
     cursor_init(ca, items, first, end);
@@ -445,61 +515,104 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
     const int32_t *ori_table = reinterpret_cast<const int32_t *>(p.oriTable);
     const int32_t *cmp_table = reinterpret_cast<const int32_t *>(p.cmpTable);
     const uint32_t slot = pw * 32u + lane;
-    int32_t row_a = -1, row_b = -1;       // logical rows handed from stage A to B, B to C
-    int32_t page_b = 0;
+    int32_t fifo_a[kLookahead];                       // stage A -> B: candidate rows, slot = tile % kLookahead
+    int32_t fifo_row[kLookahead], fifo_page[kLookahead];   // stage B -> C
+#pragma unroll
+    for (int i = 0; i < kLookahead; ++i) { fifo_a[i] = -1; fifo_row[i] = -1; fifo_page[i] = 0; }
     uint32_t issued = 0;                  // tiles whose copies have been issued
     uint32_t signalled = 0;               // tiles whose "full" barrier this thread has arrived on
 
-    for (uint32_t n = 0;; ++n) {
-        // ---- stage C inputs are last iteration's stage B outputs
-        const int32_t row_c = row_b, page_c = page_b;
-        // ---- stage B: page-table lookup for tile n-1
-        if (n >= 1 && !cb.done) {
-            row_b = row_a;
-            page_b = 0;
-            if (row_b >= 0) {
-                page_b = cb.j == 0 ? ori_table[(uint64_t)cb.it.batch * p.oriTableWidth + ((uint32_t)row_b >> 5)]
-                                   : cmp_table[(uint64_t)cb.it.batch * p.cmpTableWidth + ((uint32_t)row_b >> 5)];
+    // The loop is unrolled by the lookahead so that every value keeps its register from the load
+    // that produces it to its use kLookahead tiles later (a shifting queue would read, and so wait
+    // for, every value on every iteration).
+    bool finished = false;
+    for (uint32_t base = 0; !finished; base += (uint32_t)kLookahead) {
+#pragma unroll
+      for (int u = 0; u < kLookahead; ++u) {
+        const uint32_t n = base + (uint32_t)u;
+        const int32_t row_c = fifo_row[u], page_c = fifo_page[u], cand_b = fifo_a[u];
+        // ---- stage B: range check and page-table lookup for tile n - kLookahead
+        int32_t row_b = -1, page_b = 0;
+        if (n >= (uint32_t)kLookahead && !cb.done) {
+            const bool ori = cb.j == 0;
+            const uint32_t limit = ori ? 0x7fffffffu
+                                       : (cb.it.position < 0 ? 0u : (uint32_t)(cb.it.position + 1) / (uint32_t)RATIO);
+            if (cand_b >= 0 && (uint32_t)cand_b < limit) {
+                row_b = cand_b;
+                page_b = ori ? ori_table[(uint64_t)cb.it.batch * p.oriTableWidth + ((uint32_t)row_b >> 5)]
+                             : cmp_table[(uint64_t)cb.it.batch * p.cmpTableWidth + ((uint32_t)row_b >> 5)];
             }
+            cursor_advance(cb, items);
         }
-        // ---- stage A: logical row for tile n
-        if (!ca.done) row_a = logical_row<RATIO>(p, ca, comp, slot);
-        // ---- stage C: issue the copies of tile n-2
-        if (n >= 2) {
-            if (cc.done) break;
+        fifo_row[u] = row_b;
+        fifo_page[u] = page_b;
+        // ---- stage A: candidate row for tile n
+        int32_t cand_a = -1;
+        if (!ca.done) {
+            cand_a = candidate_row<RATIO>(p, ca, comp, slot);
+            if (cursor_advance(ca, items) && RATIO == 4) compaction_build(comp, p, ca.it, lane);
+        }
+        fifo_a[u] = cand_a;
+        // ---- stage C: issue the copies of tile n - 2 kLookahead
+        if (n >= 2u * kLookahead) {
+            if (cc.done) { finished = true; break; }
             const uint32_t stage = issued % kStages, pass = issued / kStages;
             if (!wait_phase(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
             const bool ori = cc.j == 0;
             bool valid = row_c >= 0;
             if (valid && ori && (uint32_t)page_c >= p.oriPages) valid = false;   // never read outside the original cache
-            const uint64_t src = !valid ? 0ull
-                : (ori ? p.ori + (uint64_t)(uint32_t)page_c * p.oriStride : p.cmp + (uint64_t)(uint32_t)page_c * p.cmpStride)
-                  + (uint64_t)((uint32_t)row_c & 31u) * kDim;
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
             if (lane == 0) reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + pw] = mask;
             const uint32_t tile = sm.base + kSmKv + stage * kTileBytes;
-            const uint32_t lo = (uint32_t)src, hi = (uint32_t)(src >> 32);
+            if (TMA) {
+                // lane = (group of four consecutive rows, 128-channel segment): one gather per lane
+                const uint32_t rows_per_page = (uint32_t)((ori ? p.oriStride : p.cmpStride) >> 9);
+                const int32_t gid = valid ? (int32_t)((uint32_t)page_c * rows_per_page + ((uint32_t)row_c & 31u)) : kRowsInMap;
+                const uint32_t g = lane >> 2, seg = lane & 3u;
+                const int32_t r0 = __shfl_sync(0xffffffffu, gid, 4 * g), r1 = __shfl_sync(0xffffffffu, gid, 4 * g + 1);
+                const int32_t r2 = __shfl_sync(0xffffffffu, gid, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, gid, 4 * g + 3);
+                const bool issue = ((mask >> (4u * g)) & 15u) != 0;
+                const uint32_t bytes = 512u * __popc(__ballot_sync(0xffffffffu, issue));
+                if (lane == 0) mbar_arrive_expect_tx(sm.bar(kBarFull + stage), bytes);
+                __syncwarp();
+                if (issue) {
+                    const uint32_t row0 = pw * 32u + 4u * g;
+                    tma_gather4(tile + seg * kSegBytes + (row0 >> 3) * 1024u + (row0 & 7u) * 128u, ori ? ori_map : cmp_map,
+                                (int32_t)(seg * 128u), r0, r1, r2, r3, sm.bar(kBarFull + stage));
+                }
+                ++issued;
+                signalled = issued;
+            } else {
+                const uint64_t src = !valid ? 0ull
+                    : (ori ? p.ori + (uint64_t)(uint32_t)page_c * p.oriStride : p.cmp + (uint64_t)(uint32_t)page_c * p.cmpStride)
+                      + (uint64_t)((uint32_t)row_c & 31u) * kDim;
+                const uint32_t lo = (uint32_t)src, hi = (uint32_t)(src >> 32);
 #pragma unroll 4
-            for (uint32_t r = 0; r < 32u; ++r) {
-                if (!((mask >> r) & 1u)) continue;
-                const uint64_t rsrc = ((uint64_t)__shfl_sync(0xffffffffu, hi, r) << 32) | __shfl_sync(0xffffffffu, lo, r);
-                cp_async16(tile + tile_offset(pw * 32u + r, lane, kSegBytes), reinterpret_cast<const char *>(rsrc) + lane * 16u);
-            }
-            cp_async_commit();
-            ++issued;
-            if (issued - signalled == 2) {            // keep one tile in flight behind the newest
-                cp_async_wait<1>();
-                fence_proxy_async_smem();
-                mbar_arrive(sm.bar(kBarFull + signalled % kStages));
-                ++signalled;
+                for (uint32_t r = 0; r < 32u; ++r) {
+                    if (!((mask >> r) & 1u)) continue;
+                    const uint64_t rsrc = ((uint64_t)__shfl_sync(0xffffffffu, hi, r) << 32) | __shfl_sync(0xffffffffu, lo, r);
+                    cp_async16(tile + tile_offset(pw * 32u + r, lane, kSegBytes), reinterpret_cast<const char *>(rsrc) + lane * 16u);
+                }
+                cp_async_commit();
+                ++issued;
+                if (issued - signalled == 2) {            // keep one tile in flight behind the newest
+#ifdef SHAREDKV_TIMING
+                    const long long t0 = clock64();
+                    cp_async_wait<1>();
+                    timing_add(38, clock64() - t0);
+#else
+                    cp_async_wait<1>();
+#endif
+                    fence_proxy_async_smem();
+                    mbar_arrive(sm.bar(kBarFull + signalled % kStages));
+                    ++signalled;
+                }
             }
             cursor_advance(cc, items);
         }
-        if (n >= 1 && !cb.done) cursor_advance(cb, items);
-        if (!ca.done) {
-            if (cursor_advance(ca, items) && RATIO == 4) compaction_build(comp, p, ca.it, lane);
-        }
+      }
     }
+    if (TMA) return;
     cp_async_wait<0>();
     fence_proxy_async_smem();
     while (signalled < issued) {
@@ -509,84 +622,158 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
 }
 
 // ------------------------------------------------------------------ MMA issuer (one thread)
+// Two independent instruction streams share the thread: S = K.Q^T of tile t needs the tile in
+// shared memory, the query codes of its item and a free S buffer; O = K^T.P of tile t needs the
+// P codes of tile t and a free O buffer.  Whichever is ready is issued, PV first because its
+// completion releases a ring stage to the producers.
 __device__ void mma_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
     constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
-    uint32_t gt = 0;                       // tiles issued (QK) so far
-    bool pending = false;                  // a tile whose PV has not been issued yet
-    uint32_t pending_gt = 0;
+    Cursor cq;
+    cursor_init(cq, items, first, end);
+    uint32_t qk_next = 0, pv_next = 0;     // tiles whose QK / PV have been issued
+    uint32_t q_items = 0;                  // items whose query codes have been waited for
+    bool q_ready = false;
+    volatile uint32_t *misc = sm.misc();
+    long long idle_since = clock64();
+    uint32_t idle_spins = 0;
 
-    auto issue_pv = [&](uint32_t t) -> bool {
-        const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-        if (!wait_phase(sm, kBarPReady + buf, ph)) return false;
-        if (!wait_phase(sm, kBarOFree + buf, ph ^ 1u)) return false;
-        tc_fence_after();
-        const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-        const uint32_t pb = sm.base + kSmP + buf * 2048u;
+    while (!cq.done || pv_next < qk_next) {
+        bool progressed = false;
+        if (pv_next < qk_next) {
+            const uint32_t t = pv_next, stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+            if (mbar_try_wait(sm.bar(kBarPReady + buf), ph) && mbar_try_wait(sm.bar(kBarOFree + buf), ph ^ 1u)) {
+                tc_fence_after();
+                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+                const uint32_t pb = sm.base + kSmP + buf * 2048u;
 #pragma unroll
-        for (uint32_t mb = 0; mb < 4; ++mb) {
+                for (uint32_t mb = 0; mb < 4; ++mb) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4; ++kk) {
-                const uint64_t a = smem_desc(kv + mb * kSegBytes + kk * 4096u, kSegBytes, 1024u, kSwizzle128);
-                const uint64_t b = smem_desc(pb + kk * 512u, 128u, 2048u, kSwizzleNone);
-                mma_i8(tmem + kColO + buf * 64u + mb * 16u, a, b, kIdescPV, kk);
+                    for (uint32_t kk = 0; kk < 4; ++kk) {
+                        const uint64_t a = smem_desc(kv + mb * kSegBytes + kk * 4096u, kSegBytes, 1024u, kSwizzle128);
+                        const uint64_t b = smem_desc(pb + kk * 512u, 128u, 2048u, kSwizzleNone);
+                        mma_i8(tmem + kColO + buf * 64u + mb * 16u, a, b, kIdescPV, kk);
+                    }
+                }
+                mma_commit(sm.bar(kBarOFull + buf));
+                mma_commit(sm.bar(kBarEmpty + stage));
+                ++pv_next;
+                progressed = true;
             }
         }
-        mma_commit(sm.bar(kBarOFull + buf));
-        mma_commit(sm.bar(kBarEmpty + stage));
-        return true;
-    };
-
-    for (uint32_t k = first; k < end; ++k) {
-        const Item it = load_item(items, k);
-        if (!wait_phase(sm, kBarQReady, (k - first) & 1u)) return;
-        for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
-            const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
-            if (!wait_phase(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
-            if (!wait_phase(sm, kBarSFree + buf, ph ^ 1u)) return;
-            tc_fence_after();
-            const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-            const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : 8192u);
+        if (!cq.done) {
+            const uint32_t t = qk_next, stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+            if (!q_ready && mbar_try_wait(sm.bar(kBarQReady), q_items & 1u)) q_ready = true;
+            if (q_ready && mbar_try_wait(sm.bar(kBarFull + stage), (t / kStages) & 1u) &&
+                mbar_try_wait(sm.bar(kBarSFree + buf), ph ^ 1u)) {
+                tc_fence_after();
+                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+                const uint32_t qb = sm.base + kSmQ + (cq.j == 0 ? 0u : 8192u);
 #pragma unroll
-            for (uint32_t ks = 0; ks < 16; ++ks) {
-                const uint32_t seg = ks >> 2, part = ks & 3u;
-                const uint64_t a = smem_desc(kv + seg * kSegBytes + part * 32u, 16u, 1024u, kSwizzle128);
-                const uint64_t b = smem_desc(qb + seg * 2048u + part * 32u, 16u, 1024u, kSwizzle128);
-                mma_i8(tmem + kColS + buf * 16u, a, b, kIdescQK, ks);
+                for (uint32_t ks = 0; ks < 16; ++ks) {
+                    const uint32_t seg = ks >> 2, part = ks & 3u;
+                    const uint64_t a = smem_desc(kv + seg * kSegBytes + part * 32u, 16u, 1024u, kSwizzle128);
+                    const uint64_t b = smem_desc(qb + seg * 2048u + part * 32u, 16u, 1024u, kSwizzle128);
+                    mma_i8(tmem + kColS + buf * 16u, a, b, kIdescQK, ks);
+                }
+                mma_commit(sm.bar(kBarSFull + buf));
+                ++qk_next;
+                if (cursor_advance(cq, items)) { q_ready = false; ++q_items; }
+                progressed = true;
             }
-            mma_commit(sm.bar(kBarSFull + buf));
-            if (pending && !issue_pv(pending_gt)) return;
-            pending = true; pending_gt = gt;
         }
-        if (pending) {
-            if (!issue_pv(pending_gt)) return;
-            pending = false;
+        if (progressed) {
+            idle_spins = 0;
+            continue;
+        }
+        if (idle_spins++ == 0) idle_since = clock64();
+        if ((idle_spins & 63u) == 0) {
+            if (misc[1]) return;
+            if (clock64() - idle_since > kWaitCycles) { misc[1] = 1; return; }
         }
     }
 }
 
-// ------------------------------------------------------------------ softmax / accumulate warps
-// Synchronise the four softmax warps through an mbarrier (a wait here can time out, a bar.sync cannot).
-__device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t &phase)
+// ------------------------------------------------------------------ softmax warps (0-3)
+// Synchronise one 128-thread warpgroup through an mbarrier (a wait here can time out, a bar.sync cannot).
+__device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t which, uint32_t &phase)
 {
-    mbar_arrive(sm.bar(kBarGroup));
-    const bool ok = wait_phase(sm, kBarGroup, phase);
+    mbar_arrive(sm.bar(kBarGroup + which));
+    const bool ok = wait_phase(sm, kBarGroup + which, phase);
     phase ^= 1u;
     return ok;
 }
 
-template <int RATIO, bool DEBUG>
-__device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const PlanHeader *header,
-                             const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+__device__ __forceinline__ void load_query_slice(const SharedKVArgs &p, uint32_t token, uint32_t tid, uint4 (&raw)[4])
 {
-    const uint32_t tid = threadIdx.x;              // 0..127: key within a tile, channel within a 128-block
+    const uint32_t h = tid >> 4, d0 = (tid & 15u) * 32u;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((uint64_t)token * 8u + h) * 1024u + d0 * 2u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
+}
+
+// Fold the cache scale of `kind` into this thread's 32 query channels and write the two INT8
+// code planes of head h (rows h and 8 + h of the 16-row B operand) into swizzled shared memory.
+template <bool DEBUG>
+__device__ __forceinline__ void encode_query(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm,
+                                             const uint4 (&raw)[4], uint32_t kind, uint32_t token, uint32_t tid)
+{
+    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale) + kind * 512u;
+    const uint32_t h = tid >> 4, slice = tid & 15u, d0 = slice * 32u;
+    const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float f0 = __fmul_rn(__uint_as_float(rw[i] << 16), scales[d0 + 2 * i]);
+        const float f1 = __fmul_rn(__uint_as_float(rw[i] & 0xffff0000u), scales[d0 + 2 * i + 1]);
+        amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+    }
+#pragma unroll
+    for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const float alpha = fmaxf(__fmul_rn(amax, kInv127), 1e-12f);
+    const float rcp = __frcp_rn(alpha);
+    char *qdst = sm.ptr + kSmQ + kind * 8192u;
+#pragma unroll
+    for (uint32_t c = 0; c < 2; ++c) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            int ch[4], cl[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * c + 4 * w + e;                    // channel within the slice
+                const uint32_t word = rw[i >> 1];
+                const float x = (i & 1) ? __uint_as_float(word & 0xffff0000u) : __uint_as_float(word << 16);
+                const float f = __fmul_rn(x, scales[d0 + i]);
+                const float nrm = fminf(fmaxf(__fmul_rn(f, rcp), -127.f), 127.f);
+                const float hf = rintf(nrm);
+                ch[e] = (int)hf;
+                cl[e] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
+            }
+            hi[w] = pack4(ch[0], ch[1], ch[2], ch[3]);
+            lo[w] = pack4(cl[0], cl[1], cl[2], cl[3]);
+        }
+        const uint4 vh = make_uint4(hi[0], hi[1], hi[2], hi[3]), vl = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        const uint32_t chunk = slice * 2u + c;
+        *reinterpret_cast<uint4 *>(qdst + tile_offset(h, chunk, 2048u)) = vh;
+        *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, chunk, 2048u)) = vl;
+        if (DEBUG) {
+            char *g = reinterpret_cast<char *>(dbg.qCodes) + ((uint64_t)token * 2u + kind) * 16u * 512u;
+            *reinterpret_cast<uint4 *>(g + h * 512u + chunk * 16u) = vh;
+            *reinterpret_cast<uint4 *>(g + (8u + h) * 512u + chunk * 16u) = vl;
+        }
+    }
+    if (slice == 0) reinterpret_cast<float *>(sm.ptr + kSmAlpha)[kind * 8u + h] = __fmul_rn(alpha, p.softmaxScale);
+}
+
+template <int RATIO, bool DEBUG>
+__device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
+                             uint32_t first, uint32_t end, uint32_t tmem)
+{
+    const uint32_t tid = threadIdx.x;              // 0..127: key within a tile
     const uint32_t lane = tid & 31u, warp = tid >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
-    char *ws = reinterpret_cast<char *>(p.workspace);
-    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
-    float *partials = reinterpret_cast<float *>(ws + ws_partials(p.tokens));
-    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale);
     float *red = reinterpret_cast<float *>(sm.ptr + kSmRed);
     const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha);
     volatile uint32_t *misc = sm.misc();
@@ -595,125 +782,30 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
     float sink[8];
 #pragma unroll
     for (int h = 0; h < 8; ++h) sink[h] = reinterpret_cast<const float *>(p.sinks)[h];
-    float sc[2][4];                                // cache scales of this thread's four channels
-#pragma unroll
-    for (int kind = 0; kind < 2; ++kind)
-#pragma unroll
-        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + tid];
 
-    // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
-    {
-        const uint32_t live = header->live_tokens;
-        for (uint32_t t = live + blockIdx.x; t < p.tokens; t += gridDim.x) {
-            uint4 *o = reinterpret_cast<uint4 *>(p.out) + (uint64_t)t * 512u;
-            for (uint32_t i = tid; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
-            if (p.lse && tid < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)t * 8u + tid] = 0.f;
-        }
-    }
+    Cursor cur;
+    cursor_init(cur, items, first, end);
+    uint4 raw[4];
+    if (!cur.done) load_query_slice(p, cur.it.token, tid, raw);
 
     uint32_t gt = 0;                               // tiles consumed so far by this CTA
-    for (uint32_t k = first; k < end; ++k) {
-        const Item it = load_item(items, k);
-
-        // ---------------- query encode: thread = (head, 32-channel slice)
-        {
-            const uint32_t h = tid >> 4, slice = tid & 15u, d0 = slice * 32u;
-            const uint4 *qsrc = reinterpret_cast<const uint4 *>(p.q + ((uint64_t)it.token * 8u + h) * 1024u + d0 * 2u);
-            uint4 raw[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) raw[i] = __ldg(qsrc + i);
-            const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw);
-#pragma unroll
-            for (uint32_t kind = 0; kind < 2; ++kind) {
-                float f[32];
-                float amax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float x0 = __uint_as_float(rw[i] << 16), x1 = __uint_as_float(rw[i] & 0xffff0000u);
-                    f[2 * i] = __fmul_rn(x0, scales[kind * 512 + d0 + 2 * i]);
-                    f[2 * i + 1] = __fmul_rn(x1, scales[kind * 512 + d0 + 2 * i + 1]);
-                    amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
-                }
-#pragma unroll
-                for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-                const float alpha = fmaxf(__fmul_rn(amax, kInv127), 1e-12f);
-                const float rcp = __frcp_rn(alpha);
-                int hi[32], lo[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float nrm = fminf(fmaxf(__fmul_rn(f[i], rcp), -127.f), 127.f);
-                    const float hf = rintf(nrm);
-                    hi[i] = (int)hf;
-                    lo[i] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
-                }
-                char *qdst = sm.ptr + kSmQ + kind * 8192u;
-#pragma unroll
-                for (uint32_t c = 0; c < 2; ++c) {
-                    const uint4 vh = make_uint4(pack4(hi[16 * c], hi[16 * c + 1], hi[16 * c + 2], hi[16 * c + 3]),
-                                                pack4(hi[16 * c + 4], hi[16 * c + 5], hi[16 * c + 6], hi[16 * c + 7]),
-                                                pack4(hi[16 * c + 8], hi[16 * c + 9], hi[16 * c + 10], hi[16 * c + 11]),
-                                                pack4(hi[16 * c + 12], hi[16 * c + 13], hi[16 * c + 14], hi[16 * c + 15]));
-                    const uint4 vl = make_uint4(pack4(lo[16 * c], lo[16 * c + 1], lo[16 * c + 2], lo[16 * c + 3]),
-                                                pack4(lo[16 * c + 4], lo[16 * c + 5], lo[16 * c + 6], lo[16 * c + 7]),
-                                                pack4(lo[16 * c + 8], lo[16 * c + 9], lo[16 * c + 10], lo[16 * c + 11]),
-                                                pack4(lo[16 * c + 12], lo[16 * c + 13], lo[16 * c + 14], lo[16 * c + 15]));
-                    const uint32_t chunk = slice * 2u + c;
-                    *reinterpret_cast<uint4 *>(qdst + tile_offset(h, chunk, 2048u)) = vh;
-                    *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, chunk, 2048u)) = vl;
-                    if (DEBUG) {
-                        char *g = reinterpret_cast<char *>(dbg.qCodes) + ((uint64_t)it.token * 2u + kind) * 16u * 512u;
-                        *reinterpret_cast<uint4 *>(g + h * 512u + chunk * 16u) = vh;
-                        *reinterpret_cast<uint4 *>(g + (8u + h) * 512u + chunk * 16u) = vl;
-                    }
-                }
-                if (slice == 0) reinterpret_cast<float *>(sm.ptr + kSmAlpha)[kind * 8u + h] = __fmul_rn(alpha, p.softmaxScale);
-            }
-        }
+    for (uint32_t k = 0; !cur.done; ++k) {
+        const Item it = cur.it;
+        encode_query<DEBUG>(p, dbg, sm, raw, 0, it.token, tid);
+        encode_query<DEBUG>(p, dbg, sm, raw, 1, it.token, tid);
         fence_proxy_async_smem();
         mbar_arrive(sm.bar(kBarQReady));
-        if (!group_sync(sm, group_phase)) return;
+        if (!group_sync(sm, 0, group_phase)) return;
+        // next item's query rows travel while this item's tiles are processed
+        const bool more = cur.item + 1 < cur.items_end;
+        if (more) load_query_slice(p, cur.next_lo.x, tid, raw);
 
-        // ---------------- online softmax over this item's tiles
-        float m[8], l[8], r_prev[8], acc[4][8];
+        float m[8], l[8];
 #pragma unroll
         for (int h = 0; h < 8; ++h) {
             m[h] = sink[h];
             l[h] = (tid == 0 && it.tile_begin == 0) ? 1.f : 0.f;
-            r_prev[h] = 1.f;
-#pragma unroll
-            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
         }
-        bool have_prev = false;
-        uint32_t prev_gt = 0, prev_kind = 0, prev_rec = 0;
-
-        auto drain = [&](uint32_t t, uint32_t kind, uint32_t rec) -> bool {
-            const uint32_t buf = t & 1u, ph = (t >> 1) & 1u;
-            if (!wait_phase(sm, kBarOFull + buf, ph)) return false;
-            tc_fence_after();
-            uint32_t o[4][16];
-#pragma unroll
-            for (uint32_t mb = 0; mb < 4; ++mb) tmem_ld16(tmem_lane + kColO + buf * 64u + mb * 16u, o[mb]);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(sm.bar(kBarOFree + buf));
-#pragma unroll
-            for (uint32_t mb = 0; mb < 4; ++mb) {
-                if (DEBUG && rec < dbg.maxTiles) {
-                    uint4 *g = reinterpret_cast<uint4 *>(dbg.pvAcc) + ((uint64_t)rec * 512u + mb * 128u + tid) * 4u;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[mb][4 * i], o[mb][4 * i + 1], o[mb][4 * i + 2], o[mb][4 * i + 3]);
-                }
-                const float s = kind ? sc[1][mb] : sc[0][mb];
-#pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    const float dots = __fadd_rn((float)(int)o[mb][h], __fmul_rn((float)(int)o[mb][8 + h], kInv127));
-                    const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
-                    acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r_prev[h]), pv);
-                }
-            }
-            return true;
-        };
-
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
             const uint32_t kind = j == 0 ? 0u : 1u;
             const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
@@ -721,17 +813,24 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
             const bool valid = (mask_word >> lane) & 1u;
             if (!wait_phase(sm, kBarSFull + buf, ph)) return;
+#ifdef SHAREDKV_TIMING
+            const long long t_a = clock64();
+#endif
             tc_fence_after();
             uint32_t s[16];
             tmem_ld16(tmem_lane + kColS + buf * 16u, s);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(sm.bar(kBarSFree + buf));
+#ifdef SHAREDKV_TIMING
+            const long long t_b = clock64();
+            timing_add(35, t_b - t_a);
+#endif
 
             uint32_t rec = 0;
             if (DEBUG) {
                 if (tid == 0) misc[2] = atomicAdd(reinterpret_cast<uint32_t *>(dbg.counter), 1u);
-                if (!group_sync(sm, group_phase)) return;
+                if (!group_sync(sm, 0, group_phase)) return;
                 rec = misc[2];
                 if (rec < dbg.maxTiles) {
                     if (tid == 0) {
@@ -754,21 +853,32 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             const float wmax = warp_max8(logit, lane);
             float *slot_red = red + (gt & 1u) * 32u;
             if ((lane & 3u) == 0) slot_red[warp * 8u + reduced_value_index(lane)] = wmax;
-            if (!group_sync(sm, group_phase)) return;
-            float r[8];
+            if (!group_sync(sm, 0, group_phase)) return;
+#ifdef SHAREDKV_TIMING
+            const long long t_c = clock64();
+            timing_add(36, t_c - t_b);
+#endif
+            // rescale factors of this tile go to the accumulate warps through an 8-deep ring (the softmax
+            // warps can be at most five tiles ahead of the tile being drained)
+            float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (gt & 7u) * 16u;
             int p_hi[8], p_lo[8];
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
                 const float tmax = fmaxf(fmaxf(slot_red[h], slot_red[8 + h]), fmaxf(slot_red[16 + h], slot_red[24 + h]));
                 const float mnew = fmaxf(m[h], tmax);
-                r[h] = expf(__fsub_rn(m[h], mnew));
+                const float r = expf(__fsub_rn(m[h], mnew));
                 const float w = expf(__fsub_rn(logit[h], mnew));
-                l[h] = __fadd_rn(__fmul_rn(l[h], r[h]), w);
+                l[h] = __fadd_rn(__fmul_rn(l[h], r), w);
                 const float w127 = __fmul_rn(w, 127.f);
                 const float hf = rintf(w127);
                 p_hi[h] = (int)hf;
                 p_lo[h] = (int)rintf(__fmul_rn(__fsub_rn(w127, hf), 127.f));
                 m[h] = mnew;
+                if (tid == 0) ring[h] = r;
+            }
+            if (tid == 0) {
+                reinterpret_cast<uint32_t *>(ring)[8] = rec;
+                mbar_arrive(sm.bar(kBarRescale + (gt & 7u)));
             }
             const uint4 codes = make_uint4(pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), pack4(p_hi[4], p_hi[5], p_hi[6], p_hi[7]),
                                            pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]), pack4(p_lo[4], p_lo[5], p_lo[6], p_lo[7]));
@@ -777,25 +887,115 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 reinterpret_cast<uint4 *>(dbg.pCodes)[(uint64_t)rec * 128u + tid] = codes;
             fence_proxy_async_smem();
             mbar_arrive(sm.bar(kBarPReady + buf));
-
-            if (have_prev && !drain(prev_gt, prev_kind, prev_rec)) return;
-#pragma unroll
-            for (int h = 0; h < 8; ++h) r_prev[h] = r[h];
-            have_prev = true; prev_gt = gt; prev_kind = kind; prev_rec = rec;
+#ifdef SHAREDKV_TIMING
+            timing_add(37, clock64() - t_c);
+#endif
         }
-        if (have_prev && !drain(prev_gt, prev_kind, prev_rec)) return;
 
-        // ---------------- denominators: sum the per-thread partial sums
+        // denominators: sum the per-thread partial sums, hand (m, l) to the accumulate warps
         {
             const float wsum = warp_sum8(l, lane);
-            float *slot_red = red;                      // buffer 0, after a sync of its own
-            if (!group_sync(sm, group_phase)) return;   // everyone is past the last tile's reads of `red`
-            if ((lane & 3u) == 0) slot_red[warp * 8u + reduced_value_index(lane)] = wsum;
-            if (!group_sync(sm, group_phase)) return;
+            if (!group_sync(sm, 0, group_phase)) return;   // everyone is past the last tile's reads of `red`
+            if ((lane & 3u) == 0) red[warp * 8u + reduced_value_index(lane)] = wsum;
+            if (!group_sync(sm, 0, group_phase)) return;
+            if (tid == 0) {
+                float *fin = reinterpret_cast<float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
 #pragma unroll
-            for (int h = 0; h < 8; ++h)
-                l[h] = __fadd_rn(__fadd_rn(slot_red[h], slot_red[8 + h]), __fadd_rn(slot_red[16 + h], slot_red[24 + h]));
+                for (int h = 0; h < 8; ++h) {
+                    fin[h] = m[h];
+                    fin[8 + h] = __fadd_rn(__fadd_rn(red[h], red[8 + h]), __fadd_rn(red[16 + h], red[24 + h]));
+                }
+                mbar_arrive(sm.bar(kBarItemDone + (k & 7u)));
+            }
         }
+        cursor_next_item(cur, items);
+    }
+}
+
+// ------------------------------------------------------------------ accumulate warps (4-7)
+// Thread = one channel of each of the four 128-channel blocks, all eight heads.  Drains the
+// INT32 PV accumulators of every tile into FP32 running sums, then normalises and stores the
+// token (or its partial state, merging when this CTA holds the last piece to arrive).
+template <int RATIO, bool DEBUG>
+__device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const PlanHeader *header,
+                                const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+{
+    const uint32_t tid = threadIdx.x - 128u;       // 0..127
+    const uint32_t warp = tid >> 5;
+    const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
+    char *ws = reinterpret_cast<char *>(p.workspace);
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
+    float *partials = reinterpret_cast<float *>(ws + ws_partials(p.tokens));
+    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale);
+    volatile uint32_t *misc = sm.misc();
+    uint32_t group_phase = 0;
+
+    float sc[2][4];                                // cache scales of this thread's four channels
+#pragma unroll
+    for (int kind = 0; kind < 2; ++kind)
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + tid];
+
+    // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
+    {
+        const uint32_t live = header->live_tokens;
+        for (uint32_t t = live + blockIdx.x; t < p.tokens; t += gridDim.x) {
+            uint4 *o = reinterpret_cast<uint4 *>(p.out) + (uint64_t)t * 512u;
+            for (uint32_t i = tid; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
+            if (p.lse && tid < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)t * 8u + tid] = 0.f;
+        }
+    }
+
+    Cursor cur;
+    cursor_init(cur, items, first, end);
+    uint32_t gt = 0;
+    for (uint32_t k = 0; !cur.done; ++k) {
+        const Item it = cur.it;
+        float acc[4][8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h)
+#pragma unroll
+            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
+
+        for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
+            const uint32_t buf = gt & 1u, ph = (gt >> 1) & 1u, slot = gt & 7u;
+            if (!wait_phase(sm, kBarRescale + slot, (gt >> 3) & 1u)) return;
+            const float *ring = reinterpret_cast<const float *>(sm.ptr + kSmRescale) + slot * 16u;
+            float r[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) r[h] = ring[h];
+            const uint32_t rec = DEBUG ? reinterpret_cast<const uint32_t *>(ring)[8] : 0u;
+            if (!wait_phase(sm, kBarOFull + buf, ph)) return;
+            tc_fence_after();
+            uint32_t o[4][16];
+#pragma unroll
+            for (uint32_t mb = 0; mb < 4; ++mb) tmem_ld16(tmem_lane + kColO + buf * 64u + mb * 16u, o[mb]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(sm.bar(kBarOFree + buf));
+#pragma unroll
+            for (uint32_t mb = 0; mb < 4; ++mb) {
+                if (DEBUG && rec < dbg.maxTiles) {
+                    uint4 *g = reinterpret_cast<uint4 *>(dbg.pvAcc) + ((uint64_t)rec * 512u + mb * 128u + tid) * 4u;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[mb][4 * i], o[mb][4 * i + 1], o[mb][4 * i + 2], o[mb][4 * i + 3]);
+                }
+                const float s = j == 0 ? sc[0][mb] : sc[1][mb];
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {
+                    const float dots = __fadd_rn((float)(int)o[mb][h], __fmul_rn((float)(int)o[mb][8 + h], kInv127));
+                    const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
+                    acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r[h]), pv);
+                }
+            }
+        }
+
+        // final (m, l) of this item from the softmax warps
+        if (!wait_phase(sm, kBarItemDone + (k & 7u), (k >> 3) & 1u)) return;
+        const float *fin = reinterpret_cast<const float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
+        float m[8], l[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) { m[h] = fin[h]; l[h] = fin[8 + h]; }
 
         __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.out) + (uint64_t)it.token * 4096u;
         float *lse = p.lse ? reinterpret_cast<float *>(p.lse) + (uint64_t)it.token * 8u : nullptr;
@@ -806,12 +1006,8 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 for (int mb = 0; mb < 4; ++mb)
                     out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], l[h]));
             }
-            if (lse && tid < 8) {
-                float mm = m[0], ll = l[0];
-#pragma unroll
-                for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = m[h]; ll = l[h]; }
-                lse[tid] = __fadd_rn(mm, logf(ll));
-            }
+            if (lse && tid < 8) lse[tid] = __fadd_rn(fin[tid], logf(fin[8 + tid]));
+            cursor_next_item(cur, items);
             continue;
         }
 
@@ -822,62 +1018,60 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
         for (int h = 0; h < 8; ++h)
 #pragma unroll
             for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + tid] = acc[mb][h];
-        if (tid < 8) {
-            float mm = m[0], ll = l[0];
-#pragma unroll
-            for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = m[h]; ll = l[h]; }
-            mine[4096 + tid] = mm;
-            mine[4104 + tid] = ll;
-        }
+        if (tid < 16) mine[4096 + tid] = fin[tid];
         __threadfence();
-        if (!group_sync(sm, group_phase)) return;
-        if (tid == 0) misc[2] = atomicAdd(tickets + it.token, 1u);
-        if (!group_sync(sm, group_phase)) return;
-        const uint32_t ticket = misc[2];
-        if (ticket + 1u != it.nparts) continue;
-        __threadfence();
-        float top[8], den[8];
+        if (!group_sync(sm, 1, group_phase)) return;
+        if (tid == 0) misc[3] = atomicAdd(tickets + it.token, 1u);
+        if (!group_sync(sm, 1, group_phase)) return;
+        const uint32_t ticket = misc[3];
+        if (ticket + 1u == it.nparts) {
+            __threadfence();
+            float top[8], den[8];
 #pragma unroll
-        for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
-        for (uint32_t j = 0; j < it.nparts; ++j) {
-            const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
-            const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
+            for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
+            for (uint32_t j = 0; j < it.nparts; ++j) {
+                const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+                const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
 #pragma unroll
-            for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
-        }
+                for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
+            }
 #pragma unroll
-        for (int h = 0; h < 8; ++h)
+            for (int h = 0; h < 8; ++h)
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
-        for (uint32_t j = 0; j < it.nparts; ++j) {
-            const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
-            const float *ps = partials + (uint64_t)sl * kPartialFloats;
+                for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
+            for (uint32_t j = 0; j < it.nparts; ++j) {
+                const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+                const float *ps = partials + (uint64_t)sl * kPartialFloats;
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                const float g = expf(__fsub_rn(__ldcg(ps + 4096 + h), top[h]));
-                den[h] = __fadd_rn(den[h], __fmul_rn(__ldcg(ps + 4104 + h), g));
+                for (int h = 0; h < 8; ++h) {
+                    const float g = expf(__fsub_rn(__ldcg(ps + 4096 + h), top[h]));
+                    den[h] = __fadd_rn(den[h], __fmul_rn(__ldcg(ps + 4104 + h), g));
+#pragma unroll
+                    for (int mb = 0; mb < 4; ++mb)
+                        acc[mb][h] = __fadd_rn(acc[mb][h], __fmul_rn(__ldcg(ps + h * 512 + mb * 128 + tid), g));
+                }
+            }
+#pragma unroll
+            for (int h = 0; h < 8; ++h)
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb)
-                    acc[mb][h] = __fadd_rn(acc[mb][h], __fmul_rn(__ldcg(ps + h * 512 + mb * 128 + tid), g));
+                    out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
+            if (lse && tid < 8) {
+                float mm = top[0], ll = den[0];
+#pragma unroll
+                for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = top[h]; ll = den[h]; }
+                lse[tid] = __fadd_rn(mm, logf(ll));
             }
         }
-#pragma unroll
-        for (int h = 0; h < 8; ++h)
-#pragma unroll
-            for (int mb = 0; mb < 4; ++mb)
-                out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
-        if (lse && tid < 8) {
-            float mm = top[0], ll = den[0];
-#pragma unroll
-            for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = top[h]; ll = den[h]; }
-            lse[tid] = __fadd_rn(mm, logf(ll));
-        }
+        cursor_next_item(cur, items);
     }
 }
 
 // ------------------------------------------------------------------ decode kernel
-template <int RATIO, bool DEBUG>
-__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs p, const SharedKVDebug dbg)
+template <int RATIO, bool DEBUG, bool TMA>
+__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs p, const SharedKVDebug dbg,
+                                                             const __grid_constant__ CUtensorMap ori_map,
+                                                             const __grid_constant__ CUtensorMap cmp_map)
 {
     extern __shared__ char smem_raw[];
     Shared sm;
@@ -891,17 +1085,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     volatile uint32_t *misc = sm.misc();
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < kStages; ++s) { mbar_init(sm.bar(kBarFull + s), 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
+        for (uint32_t s = 0; s < kStages; ++s) { mbar_init(sm.bar(kBarFull + s), TMA ? 4 : 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(sm.bar(kBarSFull + b), 1); mbar_init(sm.bar(kBarSFree + b), 128);
             mbar_init(sm.bar(kBarPReady + b), 128); mbar_init(sm.bar(kBarOFull + b), 1); mbar_init(sm.bar(kBarOFree + b), 128);
+            mbar_init(sm.bar(kBarGroup + b), 128);
         }
         mbar_init(sm.bar(kBarQReady), 128);
-        mbar_init(sm.bar(kBarGroup), 128);
-        misc[1] = 0; misc[2] = 0;
+        for (uint32_t i = 0; i < 8; ++i) { mbar_init(sm.bar(kBarRescale + i), 1); mbar_init(sm.bar(kBarItemDone + i), 1); }
+        misc[1] = 0; misc[2] = 0; misc[3] = 0;
         fence_mbar_init();
     }
-    if (warp == 8) {
+    if (warp == 12) {
         tmem_alloc(sm.base + kSmMisc, kTmemCols);
         tmem_relinquish();
     }
@@ -914,6 +1109,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = misc[0];
+#ifdef SHAREDKV_TIMING
+    const long long kernel_start = clock64();
+#endif
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
     const PlanHeader *header = reinterpret_cast<const PlanHeader *>(ws);
@@ -922,59 +1120,124 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     const uint32_t first = cta_first[blockIdx.x], end = cta_first[blockIdx.x + 1];
 
     if (warp < 4) {
-        softmax_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
+        softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, first, end, tmem);
     } else if (warp < 8) {
-        producer_loop<RATIO>(p, sm, items, first, end, warp - 4u, lane);
+        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
+    } else if (warp < 12) {
+        if (TMA && lane == 0) { tma_prefetch_descriptor(&ori_map); tma_prefetch_descriptor(&cmp_map); }
+        producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - 8u, lane, &ori_map, &cmp_map);
         cp_async_wait<0>();
     } else {
         if (lane == 0) mma_loop(sm, items, first, end, tmem);
         __syncwarp();
     }
+#ifdef SHAREDKV_TIMING
+    timing_add(39, clock64() - kernel_start);
+#endif
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && misc[1])
         reinterpret_cast<PlanHeader *>(const_cast<char *>(ws))->status = kStatusWaitTimeout;
-    if (warp == 8) {
+    if (warp == 12) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled()
+{
+    static std::atomic<void *> cached{nullptr};
+    void *fn = cached.load(std::memory_order_acquire);
+    if (fn == nullptr) {
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status) != cudaSuccess ||
+            status != cudaDriverEntryPointSuccess)
+            return nullptr;
+        cached.store(fn, std::memory_order_release);
+    }
+    return reinterpret_cast<EncodeTiled>(fn);
+}
+
+// 2-D view of a paged cache for row gathers: [kRowsInMap rows, 512 bytes], 512-byte pitch; row id =
+// page * (page stride / 512) + row in page.  Box = one 128-byte column block of one row.
+bool make_row_map(CUtensorMap *map, uint64_t base)
+{
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {kDim, (cuuint64_t)kRowsInMap};
+    const cuuint64_t strides[1] = {kDim};
+    const cuuint32_t box[2] = {128, 1};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, reinterpret_cast<void *>(base), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int RATIO, bool DEBUG, bool TMA>
+cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const CUtensorMap &ori_map,
+                          const CUtensorMap &cmp_map, uint32_t grid, cudaStream_t stream, int device)
+{
+    // the opt-in to > 48 KB of dynamic shared memory is per device and per kernel
+    static std::atomic<uint64_t> configured{0};
+    const uint64_t bit = 1ull << (device & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<RATIO, DEBUG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    decode_kernel<RATIO, DEBUG, TMA><<<grid, kThreads, kSmemBytes, stream>>>(a, d, ori_map, cmp_map);
+    return cudaGetLastError();
 }
 
 template <int RATIO>
 int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debug, int sms)
 {
     uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
-    if (debug && debug->reserved && debug->reserved < grid) grid = debug->reserved;
+    const uint32_t cap = debug ? (debug->reserved & 0x7fffffffu) : 0u;      // test hook: fewer CTAs
+    if (cap && cap < grid) grid = cap;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    // Row gathers by TMA need page strides that are whole rows and row ids that fit the map;
+    // anything else takes the cp.async producer.
+    CUtensorMap ori_map, cmp_map;
+    bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 && !(debug && (debug->reserved & 0x80000000u)) &&
+               (uint64_t)a.oriPages * (a.oriStride / kDim) < (uint64_t)kRowsInMap && a.cmpStride / kDim < 65536;
+    if (tma) tma = make_row_map(&ori_map, a.ori) && make_row_map(&cmp_map, a.cmp);
+    if (!tma) { memset(&ori_map, 0, sizeof(ori_map)); memset(&cmp_map, 0, sizeof(cmp_map)); }
     plan_kernel<RATIO><<<1, kPlanThreads, 0, stream>>>(a, grid);
-    cudaError_t e = cudaGetLastError();
+    e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     SharedKVDebug d = {};
-    int device = 0;
-    e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return (int)e;
-    // the opt-in to > 48 KB of dynamic shared memory is per device and per kernel
-    static std::atomic<uint64_t> configured[2];
-    const uint64_t bit = 1ull << (device & 63);
     if (debug) {
         d = *debug;
-        if (!(configured[1].load(std::memory_order_relaxed) & bit)) {
-            e = cudaFuncSetAttribute(decode_kernel<RATIO, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-            if (e != cudaSuccess) return (int)e;
-            configured[1].fetch_or(bit, std::memory_order_relaxed);
-        }
-        decode_kernel<RATIO, true><<<grid, kThreads, kSmemBytes, stream>>>(a, d);
+        e = tma ? launch_decode<RATIO, true, true>(a, d, ori_map, cmp_map, grid, stream, device)
+                : launch_decode<RATIO, true, false>(a, d, ori_map, cmp_map, grid, stream, device);
     } else {
-        if (!(configured[0].load(std::memory_order_relaxed) & bit)) {
-            e = cudaFuncSetAttribute(decode_kernel<RATIO, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-            if (e != cudaSuccess) return (int)e;
-            configured[0].fetch_or(bit, std::memory_order_relaxed);
-        }
-        decode_kernel<RATIO, false><<<grid, kThreads, kSmemBytes, stream>>>(a, d);
+        e = tma ? launch_decode<RATIO, false, true>(a, d, ori_map, cmp_map, grid, stream, device)
+                : launch_decode<RATIO, false, false>(a, d, ori_map, cmp_map, grid, stream, device);
     }
-    return (int)cudaGetLastError();
+    return (int)e;
 }
 
 }  // namespace
+
+#ifdef SHAREDKV_TIMING
+extern "C" __attribute__((visibility("default"))) int sharedkv_timing_read(unsigned long long *host, int reset)
+{
+    cudaError_t e = cudaMemcpyFromSymbol(host, g_wait_cycles, sizeof(g_wait_cycles));
+    if (e == cudaSuccess && reset) {
+        static unsigned long long zeros[kMaxCtas][160];
+        e = cudaMemcpyToSymbol(g_wait_cycles, zeros, sizeof(zeros));
+    }
+    return (int)e;
+}
+#endif
 
 uint64_t workspace_bytes(uint32_t tokens)
 {

@@ -35,6 +35,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return done != 0;
 }
+// One arrival that also announces `bytes` of asynchronous (TMA) traffic to the current phase.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void fence_mbar_init()
 {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -53,6 +58,23 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait()
 {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------- TMA row gather
+// Four rows (any row indices) x one 128-byte column block of a 2-D tensor into four consecutive
+// 128-byte rows of shared memory; completion is counted in bytes on `bar`.  Rows outside the
+// tensor are filled with zeros.  The tensor map's box is {128 bytes, 1 row}, 128-byte swizzle.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tensor_map, int32_t x, int32_t r0, int32_t r1,
+                                            int32_t r2, int32_t r3, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(tensor_map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_descriptor(const void *tensor_map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
 
 // Make generic-proxy shared-memory writes visible to the async proxy (tcgen05.mma operand reads).

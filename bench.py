@@ -183,6 +183,8 @@ def time_cpu_path(lengths, ratios, budget_s, threads):
     g = torch.Generator().manual_seed(7)
     kinds = sorted(set(ratios))
     done, rows, spent = 0, 0, 0.0
+    if budget_s <= 0:
+        return None, None, 0
     oracle.attention_tiled(cpu_sample_case(kinds[0], [4096] * 2, 1), scale, scale)     # warm the thread pool
     while spent < budget_s:
         for ratio in kinds:
@@ -400,9 +402,10 @@ def main():
         "per_gpu_value": value / world, "kv_gbs": kv_gbs, "kv_gbs_per_gpu": kv_gbs / world,
         "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}> (+ its plan kernel)"),
         "roofline_other": {f"decode_kernel<{r}>": v for r, v in roof.items() if r != dominant},
-        "cpu_baseline": {"value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": "port",
-                         "sample": f"{cpu_n} queries, batches of 8 requests per layer kind drawn from rank 0's requests",
-                         "kv_gbs": cpu_rows * ROW_BYTES / 1e9},
+        "cpu_baseline": None if not cpu_n else {
+            "value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"{cpu_n} queries, batches of 8 requests per layer kind drawn from rank 0's requests",
+            "kv_gbs": cpu_rows * ROW_BYTES / 1e9},
         "e2e": e2e, "gpu_launches": 2 * len(marks), "clocks": clocks,
     }
     print(json.dumps(line))

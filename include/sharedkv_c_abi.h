@@ -138,6 +138,9 @@ SHAREDKV_API int sharedkv_cache_write(uint64_t args, uint32_t blocks, int32_t de
  *   pvAcc     INT32 [maxTiles, 512, 16] PV accumulators
  *   qCodes    INT8  [tokens, 2, 16, 512] query code planes per cache kind
  *   counter   UINT32 [1]                 tiles dumped (zeroed by the caller)
+ * `reserved`: bits 0-30, when non-zero, cap the number of CTAs (1 = every token is processed as
+ * one piece, like the reference's single running state); bit 31 selects the cp.async row
+ * gather instead of the TMA gather.
  * No counterpart in the reference; its oracle computes these inline
  * (npu_sparse_attn_sharedkv_int8/reference.py:287-289,310-313). */
 typedef struct SharedKVDebug {

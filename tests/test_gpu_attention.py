@@ -62,10 +62,13 @@ def test_golden_cases(name):
     assert torch.equal(again, out)                      # deterministic across launches
 
 
+@pytest.mark.parametrize("stride,offset", [(PAGE_STRIDE, 16384), (16384 + 48, 16)])
 @pytest.mark.parametrize("name", ("config0_c4", "mixed_c128", "real_c4"))
-def test_page_stride_and_offset_views(name):
+def test_page_stride_and_offset_views(name, stride, offset):
+    """Compact-layout views (whole-row strides: TMA row gather) and strides that are not a
+    multiple of 512 bytes (cp.async row gather)."""
     case, ori_scale, cmp_scale, z = load_case(name)
-    dev = to_device(case, DEVICE, stride=PAGE_STRIDE, offset=16384)
+    dev = to_device(case, DEVICE, stride=stride, offset=offset)
     op = prepared(dev, ori_scale, cmp_scale, return_lse=True)
     out = op.run()
     torch.cuda.synchronize()
@@ -98,14 +101,15 @@ def run_debug(op, max_tiles, ctas=0):
     return {k: v.cpu() for k, v in buffers.items()}
 
 
+@pytest.mark.parametrize("legacy_gather", [False, True])
 @pytest.mark.parametrize("name,ctas", [("config0_c4", 1), ("holes_c4", 1), ("short_c4", 1), ("mixed_c128", 1),
                                        ("real_c128", 1), ("config0_c4", 0), ("mixed_c128", 0), ("short_c4", 5)])
-def test_integer_stages_are_exact(name, ctas):
+def test_integer_stages_are_exact(name, ctas, legacy_gather):
     case, ori_scale, cmp_scale, z = load_case(name)
     trace = oracle.Trace()
     oracle.attention_tiled(case, ori_scale, cmp_scale, trace=trace)
     op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
-    dump = run_debug(op, max_tiles=len(trace.tiles) + 64, ctas=ctas)
+    dump = run_debug(op, max_tiles=len(trace.tiles) + 64, ctas=ctas | (0x80000000 if legacy_gather else 0))
     out, lse = op.out.cpu(), op.lse.cpu()
     check_against_reference(out, lse, z, case, (ori_scale, cmp_scale), ctas=ctas or None)
 
