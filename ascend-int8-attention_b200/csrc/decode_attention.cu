@@ -57,7 +57,8 @@ constexpr uint32_t kTileKeys = 128;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
-constexpr uint32_t kThreads = 416;                        // 4 softmax + 4 accumulate + 4 producer + 1 MMA warps
+constexpr uint32_t kThreads = 544;                        // 8 softmax + 4 accumulate + 4 producer + 1 MMA warps
+constexpr uint32_t kWarpProducer = 12, kWarpMma = 16;
 constexpr uint32_t kMaxCtas = 160;
 constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
@@ -70,15 +71,16 @@ constexpr uint32_t kSmKv = 0;
 constexpr uint32_t kSmQ = kSmKv + kStages * kTileBytes;      // 2 kinds x 16 rows x 512 B, swizzled
 constexpr uint32_t kSmP = kSmQ + 2 * 8192;                   // 2 buffers x 128 keys x 16 B
 constexpr uint32_t kSmScale = kSmP + 2 * 2048;               // FP32 [2][512]
-constexpr uint32_t kSmMask = kSmScale + 2 * 2048;            // UINT32 [stages][4]
-constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2][4 warps][8]
+constexpr uint32_t kSmMask = kSmScale + 2 * 2048;            // UINT32 [stages][4]: bit k of the 128-bit word = slot k holds a key
+constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2 halves][2 parities][4 warps][4]
 constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [2 kinds][8]: alpha * softmax_scale
 constexpr uint32_t kSmRescale = kSmAlpha + 64;               // [8 tiles][16]: r[8], debug record, pad
 constexpr uint32_t kSmFinal = kSmRescale + 8 * 64;           // [8 items][16]: m[8], l[8]
-constexpr uint32_t kSmBar = kSmFinal + 8 * 64;               // mbarriers
+constexpr uint32_t kSmItems = kSmFinal + 8 * 64;             // producers: per warp a ring of 16 decoded work items
+constexpr uint32_t kSmBar = kSmItems + 4 * 16 * 32;          // mbarriers
 constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kBarPReady = 10, kBarOFull = 12,
-                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17 /* +1 for the accumulate warps */,
-                   kBarRescale = 19 /* x8 */, kBarItemDone = 27 /* x8 */, kNumBars = 35;
+                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17 /* x4: softmax halves, all softmax, all accumulate */,
+                   kBarRescale = 21 /* x8 */, kBarItemDone = 29 /* x8 */, kNumBars = 37;
 constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words
 constexpr uint32_t kSmemBytes = kSmMisc + 16 + 1024;         // + alignment slack
 static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
@@ -268,12 +270,12 @@ struct Shared {
 
 #ifdef SHAREDKV_TIMING
 // Development aid (not built by default): cycles spent waiting, per CTA, per role and barrier.
-__device__ unsigned long long g_wait_cycles[kMaxCtas][160];
+__device__ unsigned long long g_wait_cycles[kMaxCtas][240];
 __device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
 {
     const uint32_t warp = threadIdx.x >> 5;
     if ((threadIdx.x & 31u) == 0 && (warp & 3u) == 0)
-        g_wait_cycles[blockIdx.x][(warp >> 2) * 40u + slot] += (unsigned long long)cycles;
+        atomicAdd(&g_wait_cycles[blockIdx.x][(warp >> 2) * 40u + slot], (unsigned long long)cycles);
 }
 #endif
 
@@ -415,6 +417,38 @@ __device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items)
     cursor_prefetch(c, items);
     return true;
 }
+// Trailing cursor of a producer warp: walks the same tiles as a leading Cursor, a bounded
+// number of items behind it, and takes the descriptors from the warp's shared-memory ring the
+// leader fills (every lane writes and later reads its own copy, so no synchronisation is involved).
+struct Follower {
+    uint32_t item, items_end, j, tile_end, batch;
+    int32_t position;
+    bool done;
+};
+__device__ __forceinline__ void ring_put(const Shared &sm, uint32_t pw, uint32_t index, const Item &it)
+{
+    uint4 *dst = reinterpret_cast<uint4 *>(sm.ptr + kSmItems) + (pw * 16u + (index & 15u)) * 2u;
+    dst[0] = make_uint4(it.token, it.batch, (uint32_t)it.position, it.tile_begin);
+    dst[1] = make_uint4(it.tile_end, it.part, it.nparts, it.first_cta);
+}
+__device__ __forceinline__ void follower_load(Follower &f, const Shared &sm, uint32_t pw)
+{
+    const uint4 *src = reinterpret_cast<const uint4 *>(sm.ptr + kSmItems) + (pw * 16u + (f.item & 15u)) * 2u;
+    const uint4 a = src[0], b = src[1];
+    f.batch = a.y; f.position = (int32_t)a.z; f.j = a.w; f.tile_end = b.x;
+}
+__device__ __forceinline__ void follower_init(Follower &f, const Shared &sm, uint32_t pw, uint32_t first, uint32_t end)
+{
+    f.item = first; f.items_end = end; f.done = first >= end;
+    f.j = f.tile_end = f.batch = 0; f.position = 0;
+    if (!f.done) follower_load(f, sm, pw);
+}
+__device__ __forceinline__ void follower_advance(Follower &f, const Shared &sm, uint32_t pw)
+{
+    if (++f.j < f.tile_end) return;
+    if (++f.item >= f.items_end) { f.done = true; return; }
+    follower_load(f, sm, pw);
+}
 // Skip whatever is left of the current item.
 __device__ __forceinline__ void cursor_next_item(Cursor &c, const Item *items)
 {
@@ -467,7 +501,7 @@ __device__ __forceinline__ uint32_t compaction_slot(const Compaction &k, uint32_
     return chunk * 32u + (bit & 31u);
 }
 
-// Stage A of the producer: candidate logical row of this lane's slot in the cursor's tile.
+// Stage A of the producer: candidate logical row of slot `slot` in the cursor's tile.
 // Values read from the top-k array are returned unchecked (stage B range-checks them, so
 // that the load is not consumed here); every other path returns a valid row or -1.
 template <int RATIO>
@@ -490,24 +524,32 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
     return s < p.topk ? ix[s] : -1;
 }
 
-// Producer warps.  Three stages, each `kLookahead` tiles behind the previous one, so that the
-// two dependent global reads in front of a row copy (top-k entry -> page-table entry -> row)
-// are issued several tiles before their results are needed:
+// Producer warps (four, one per SM sub-partition: the rate at which a warp can hand row fetches to
+// the TMA unit is limited per warp).  Warp w owns key slots 32 w .. 32 w + 31 of every tile, lane =
+// slot.  Three stages, each `kLookahead` tiles behind the previous one, so that the two dependent
+// global reads in front of a row fetch (top-k entry -> page-table entry -> row) are issued several
+// tiles before their results are needed:
 //   A  candidate logical row of this lane's slot          (tile n)
 //   B  range check + page-table lookup                    (tile n - kLookahead)
-//   C  16-byte cp.async copies of the 128 rows of a tile  (tile n - 2 kLookahead)
+//   C  row fetch into the ring stage                      (tile n - 2 kLookahead)
+// The loop is unrolled by the lookahead so that every value keeps its register from the load that
+// produces it to its use (a shifting queue would read, and so wait for, every value each iteration).
+// Row fetch: one TMA gather of four consecutive slots x one 128-channel segment per lane
+// (lane = 4 * group + segment), or 16-byte cp.async copies when the page strides rule TMA out.
 constexpr int kLookahead = 4;
-
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
 template <int RATIO, bool TMA>
 __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, uint32_t first, uint32_t end,
-                              uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map)
+                              uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
+                              const CUtensorMap *cmp_page_map)
 {
-    Cursor ca, cb, cc;
+    Cursor ca;
     cursor_init(ca, items, first, end);
-    cursor_init(cb, items, first, end);
-    cursor_init(cc, items, first, end);
+    if (!ca.done) ring_put(sm, pw, ca.item, ca.it);
+    Follower cb, cc;
+    follower_init(cb, sm, pw, first, end);
+    follower_init(cc, sm, pw, first, end);
     Compaction comp;
     comp.active = false; comp.mask = comp.inclusive = comp.total = 0;
     if (RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
@@ -515,59 +557,69 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
     const int32_t *ori_table = reinterpret_cast<const int32_t *>(p.oriTable);
     const int32_t *cmp_table = reinterpret_cast<const int32_t *>(p.cmpTable);
     const uint32_t slot = pw * 32u + lane;
-    int32_t fifo_a[kLookahead];                       // stage A -> B: candidate rows, slot = tile % kLookahead
-    int32_t fifo_row[kLookahead], fifo_page[kLookahead];   // stage B -> C
+    int32_t cand[kLookahead];             // stage A -> B, index = tile % kLookahead
+    int32_t page[kLookahead];             // stage B -> C: page id ...
+    int32_t offs[kLookahead];             // ... and row within the page, or -1 when the slot holds no key
 #pragma unroll
-    for (int i = 0; i < kLookahead; ++i) { fifo_a[i] = -1; fifo_row[i] = -1; fifo_page[i] = 0; }
-    uint32_t issued = 0;                  // tiles whose copies have been issued
-    uint32_t signalled = 0;               // tiles whose "full" barrier this thread has arrived on
+    for (int u = 0; u < kLookahead; ++u) { cand[u] = -1; page[u] = 0; offs[u] = -1; }
+    uint32_t issued = 0;                  // tiles whose fetches have been issued
+    uint32_t signalled = 0;               // cp.async path: tiles whose "full" barrier this thread has arrived on
 
-    // The loop is unrolled by the lookahead so that every value keeps its register from the load
-    // that produces it to its use kLookahead tiles later (a shifting queue would read, and so wait
-    // for, every value on every iteration).
     bool finished = false;
     for (uint32_t base = 0; !finished; base += (uint32_t)kLookahead) {
 #pragma unroll
       for (int u = 0; u < kLookahead; ++u) {
         const uint32_t n = base + (uint32_t)u;
-        const int32_t row_c = fifo_row[u], page_c = fifo_page[u], cand_b = fifo_a[u];
+        const int32_t page_c = page[u], off_c = offs[u];
         // ---- stage B: range check and page-table lookup for tile n - kLookahead
-        int32_t row_b = -1, page_b = 0;
+        int32_t off_b = -1, page_b = 0;
         if (n >= (uint32_t)kLookahead && !cb.done) {
             const bool ori = cb.j == 0;
             const uint32_t limit = ori ? 0x7fffffffu
-                                       : (cb.it.position < 0 ? 0u : (uint32_t)(cb.it.position + 1) / (uint32_t)RATIO);
-            if (cand_b >= 0 && (uint32_t)cand_b < limit) {
-                row_b = cand_b;
-                page_b = ori ? ori_table[(uint64_t)cb.it.batch * p.oriTableWidth + ((uint32_t)row_b >> 5)]
-                             : cmp_table[(uint64_t)cb.it.batch * p.cmpTableWidth + ((uint32_t)row_b >> 5)];
+                                       : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
+            const int32_t c = cand[u];
+            if (c >= 0 && (uint32_t)c < limit) {
+                off_b = c & 31;
+                page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
+                             : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
             }
-            cursor_advance(cb, items);
+            follower_advance(cb, sm, pw);
         }
-        fifo_row[u] = row_b;
-        fifo_page[u] = page_b;
+        page[u] = page_b;
+        offs[u] = off_b;
         // ---- stage A: candidate row for tile n
         int32_t cand_a = -1;
         if (!ca.done) {
             cand_a = candidate_row<RATIO>(p, ca, comp, slot);
-            if (cursor_advance(ca, items) && RATIO == 4) compaction_build(comp, p, ca.it, lane);
+            if (cursor_advance(ca, items)) {
+                ring_put(sm, pw, ca.item, ca.it);
+                if (RATIO == 4) compaction_build(comp, p, ca.it, lane);
+            }
         }
-        fifo_a[u] = cand_a;
-        // ---- stage C: issue the copies of tile n - 2 kLookahead
+        cand[u] = cand_a;
+        // ---- stage C: fetch the rows of tile n - 2 kLookahead
         if (n >= 2u * kLookahead) {
             if (cc.done) { finished = true; break; }
             const uint32_t stage = issued % kStages, pass = issued / kStages;
             if (!wait_phase(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
             const bool ori = cc.j == 0;
-            bool valid = row_c >= 0;
-            if (valid && ori && (uint32_t)page_c >= p.oriPages) valid = false;   // never read outside the original cache
+            const bool valid = off_c >= 0 && !(ori && (uint32_t)page_c >= p.oriPages);   // never read outside the original cache
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
             if (lane == 0) reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + pw] = mask;
             const uint32_t tile = sm.base + kSmKv + stage * kTileBytes;
-            if (TMA) {
-                // lane = (group of four consecutive rows, 128-channel segment): one gather per lane
+            if (TMA && RATIO == 128 && !ori) {
+                // the 32 slots of this warp are one page of the compressed cache: four 4 KB boxes
+                const bool any = mask != 0;
+                const int32_t page_id = __shfl_sync(0xffffffffu, page_c, 0);      // slot 32 w is the first to be valid
+                if (lane == 0) mbar_arrive_expect_tx(sm.bar(kBarFull + stage), any ? 16384u : 0u);
+                __syncwarp();
+                if (any && lane < 4)
+                    tma_page_segment(tile + lane * kSegBytes + pw * 4096u, cmp_page_map, (int32_t)(lane * 128u), page_id,
+                                     sm.bar(kBarFull + stage));
+                ++issued;
+            } else if (TMA) {
                 const uint32_t rows_per_page = (uint32_t)((ori ? p.oriStride : p.cmpStride) >> 9);
-                const int32_t gid = valid ? (int32_t)((uint32_t)page_c * rows_per_page + ((uint32_t)row_c & 31u)) : kRowsInMap;
+                const int32_t gid = valid ? (int32_t)((uint32_t)page_c * rows_per_page + (uint32_t)off_c) : kRowsInMap;
                 const uint32_t g = lane >> 2, seg = lane & 3u;
                 const int32_t r0 = __shfl_sync(0xffffffffu, gid, 4 * g), r1 = __shfl_sync(0xffffffffu, gid, 4 * g + 1);
                 const int32_t r2 = __shfl_sync(0xffffffffu, gid, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, gid, 4 * g + 3);
@@ -581,11 +633,10 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                                 (int32_t)(seg * 128u), r0, r1, r2, r3, sm.bar(kBarFull + stage));
                 }
                 ++issued;
-                signalled = issued;
             } else {
                 const uint64_t src = !valid ? 0ull
                     : (ori ? p.ori + (uint64_t)(uint32_t)page_c * p.oriStride : p.cmp + (uint64_t)(uint32_t)page_c * p.cmpStride)
-                      + (uint64_t)((uint32_t)row_c & 31u) * kDim;
+                      + (uint64_t)(uint32_t)off_c * kDim;
                 const uint32_t lo = (uint32_t)src, hi = (uint32_t)(src >> 32);
 #pragma unroll 4
                 for (uint32_t r = 0; r < 32u; ++r) {
@@ -596,19 +647,13 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 cp_async_commit();
                 ++issued;
                 if (issued - signalled == 2) {            // keep one tile in flight behind the newest
-#ifdef SHAREDKV_TIMING
-                    const long long t0 = clock64();
                     cp_async_wait<1>();
-                    timing_add(38, clock64() - t0);
-#else
-                    cp_async_wait<1>();
-#endif
                     fence_proxy_async_smem();
                     mbar_arrive(sm.bar(kBarFull + signalled % kStages));
                     ++signalled;
                 }
             }
-            cursor_advance(cc, items);
+            follower_advance(cc, sm, pw);
         }
       }
     }
@@ -695,8 +740,11 @@ __device__ void mma_loop(const Shared &sm, const Item *items, uint32_t first, ui
     }
 }
 
-// ------------------------------------------------------------------ softmax warps (0-3)
-// Synchronise one 128-thread warpgroup through an mbarrier (a wait here can time out, a bar.sync cannot).
+// ------------------------------------------------------------------ softmax warps (0-7)
+// Two halves of four warps.  Thread (half, key) owns heads 4 half .. 4 half + 3 of key `key` of
+// every tile: columns 4 half + i (high plane) and 8 + 4 half + i (low plane) of S.
+
+// Wait-capable rendezvous of `which`'s threads (an mbarrier wait can time out, a bar.sync cannot).
 __device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t which, uint32_t &phase)
 {
     mbar_arrive(sm.bar(kBarGroup + which));
@@ -705,22 +753,45 @@ __device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t which, uin
     return ok;
 }
 
-__device__ __forceinline__ void load_query_slice(const SharedKVArgs &p, uint32_t token, uint32_t tid, uint4 (&raw)[4])
+// Reduce four per-thread values across the 32 lanes; afterwards lane 8 i (i = 0..3) holds value i.
+template <bool MAX>
+__device__ __forceinline__ float warp_reduce4(const float (&v)[4], uint32_t lane)
 {
-    const uint32_t h = tid >> 4, d0 = (tid & 15u) * 32u;
+    auto op = [](float a, float b) { return MAX ? fmaxf(a, b) : a + b; };
+    float a[2], c;
+    const bool up16 = lane & 16u, up8 = lane & 8u;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float send = up16 ? v[i] : v[i + 2], keep = up16 ? v[i + 2] : v[i];
+        a[i] = op(keep, __shfl_xor_sync(0xffffffffu, send, 16));
+    }
+    {
+        const float send = up8 ? a[0] : a[1], keep = up8 ? a[1] : a[0];
+        c = op(keep, __shfl_xor_sync(0xffffffffu, send, 8));
+    }
+    c = op(c, __shfl_xor_sync(0xffffffffu, c, 4));
+    c = op(c, __shfl_xor_sync(0xffffffffu, c, 2));
+    c = op(c, __shfl_xor_sync(0xffffffffu, c, 1));
+    return c;   // value index = 2 * bit4 + bit3 of the lane
+}
+
+__device__ __forceinline__ void load_query_slice(const SharedKVArgs &p, uint32_t token, uint32_t t, uint4 (&raw)[4])
+{
+    const uint32_t h = t >> 4, d0 = (t & 15u) * 32u;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((uint64_t)token * 8u + h) * 1024u + d0 * 2u);
 #pragma unroll
     for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
 }
 
-// Fold the cache scale of `kind` into this thread's 32 query channels and write the two INT8
-// code planes of head h (rows h and 8 + h of the 16-row B operand) into swizzled shared memory.
+// Fold the cache scale of `kind` into this thread's 32 query channels (head t / 16, channels
+// 32 (t % 16) ..) and write the two INT8 code planes of that head (rows h and 8 + h of the
+// 16-row B operand) into swizzled shared memory.
 template <bool DEBUG>
 __device__ __forceinline__ void encode_query(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm,
-                                             const uint4 (&raw)[4], uint32_t kind, uint32_t token, uint32_t tid)
+                                             const uint4 (&raw)[4], uint32_t kind, uint32_t token, uint32_t t)
 {
     const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale) + kind * 512u;
-    const uint32_t h = tid >> 4, slice = tid & 15u, d0 = slice * 32u;
+    const uint32_t h = t >> 4, slice = t & 15u, d0 = slice * 32u;
     const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw);
     float amax = 0.f;
 #pragma unroll
@@ -771,40 +842,40 @@ template <int RATIO, bool DEBUG>
 __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
                              uint32_t first, uint32_t end, uint32_t tmem)
 {
-    const uint32_t tid = threadIdx.x;              // 0..127: key within a tile
-    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    const uint32_t half = threadIdx.x >> 7;        // 0: heads 0-3, 1: heads 4-7
+    const uint32_t key = threadIdx.x & 127u;       // key within a tile
+    const uint32_t lane = key & 31u, warp = key >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
-    float *red = reinterpret_cast<float *>(sm.ptr + kSmRed);
+    float *red = reinterpret_cast<float *>(sm.ptr + kSmRed) + half * 32u;     // [2 parities][4 warps][4], per half
     const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha);
     volatile uint32_t *misc = sm.misc();
-    uint32_t group_phase = 0;
+    uint32_t group_phase = 0, all_phase = 0;
 
-    float sink[8];
+    float sink[4];
 #pragma unroll
-    for (int h = 0; h < 8; ++h) sink[h] = reinterpret_cast<const float *>(p.sinks)[h];
+    for (int i = 0; i < 4; ++i) sink[i] = reinterpret_cast<const float *>(p.sinks)[half * 4u + i];
 
     Cursor cur;
     cursor_init(cur, items, first, end);
     uint4 raw[4];
-    if (!cur.done) load_query_slice(p, cur.it.token, tid, raw);
+    if (!cur.done) load_query_slice(p, cur.it.token, key, raw);
 
     uint32_t gt = 0;                               // tiles consumed so far by this CTA
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
-        encode_query<DEBUG>(p, dbg, sm, raw, 0, it.token, tid);
-        encode_query<DEBUG>(p, dbg, sm, raw, 1, it.token, tid);
+        // each half encodes the query against one cache kind's scales
+        encode_query<DEBUG>(p, dbg, sm, raw, half, it.token, key);
         fence_proxy_async_smem();
         mbar_arrive(sm.bar(kBarQReady));
-        if (!group_sync(sm, 0, group_phase)) return;
         // next item's query rows travel while this item's tiles are processed
-        const bool more = cur.item + 1 < cur.items_end;
-        if (more) load_query_slice(p, cur.next_lo.x, tid, raw);
+        if (cur.item + 1 < cur.items_end) load_query_slice(p, cur.next_lo.x, key, raw);
+        if (!wait_phase(sm, kBarQReady, k & 1u)) return;     // both halves' alphas are written
 
-        float m[8], l[8];
+        float m[4], l[4];
 #pragma unroll
-        for (int h = 0; h < 8; ++h) {
-            m[h] = sink[h];
-            l[h] = (tid == 0 && it.tile_begin == 0) ? 1.f : 0.f;
+        for (int i = 0; i < 4; ++i) {
+            m[i] = sink[i];
+            l[i] = (key == 0 && it.tile_begin == 0) ? 1.f : 0.f;
         }
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
             const uint32_t kind = j == 0 ? 0u : 1u;
@@ -813,97 +884,94 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
             const bool valid = (mask_word >> lane) & 1u;
             if (!wait_phase(sm, kBarSFull + buf, ph)) return;
-#ifdef SHAREDKV_TIMING
-            const long long t_a = clock64();
-#endif
             tc_fence_after();
-            uint32_t s[16];
-            tmem_ld16(tmem_lane + kColS + buf * 16u, s);
+            uint32_t s_hi[4], s_lo[4];
+            tmem_ld4(tmem_lane + kColS + buf * 16u + half * 4u, s_hi);
+            tmem_ld4(tmem_lane + kColS + buf * 16u + 8u + half * 4u, s_lo);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(sm.bar(kBarSFree + buf));
-#ifdef SHAREDKV_TIMING
-            const long long t_b = clock64();
-            timing_add(35, t_b - t_a);
-#endif
 
             uint32_t rec = 0;
             if (DEBUG) {
-                if (tid == 0) misc[2] = atomicAdd(reinterpret_cast<uint32_t *>(dbg.counter), 1u);
-                if (!group_sync(sm, 0, group_phase)) return;
+                if (threadIdx.x == 0) misc[2] = atomicAdd(reinterpret_cast<uint32_t *>(dbg.counter), 1u);
+                if (!group_sync(sm, 2, all_phase)) return;
                 rec = misc[2];
+                if (!group_sync(sm, 2, all_phase)) return;      // everyone has read the record before the next is drawn
                 if (rec < dbg.maxTiles) {
-                    if (tid == 0) {
+                    if (threadIdx.x == 0) {
                         int32_t *info = reinterpret_cast<int32_t *>(dbg.tileInfo) + (uint64_t)rec * 4u;
                         info[0] = (int32_t)it.token; info[1] = (int32_t)kind; info[2] = (int32_t)(kind ? j - 1u : 0u); info[3] = (int32_t)it.part;
                     }
-                    if (lane == 0) reinterpret_cast<uint32_t *>(dbg.validMask)[(uint64_t)rec * 4u + warp] = mask_word;
-                    uint4 *g = reinterpret_cast<uint4 *>(dbg.qkAcc) + ((uint64_t)rec * 128u + tid) * 4u;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
+                    if (half == 0 && lane == 0) reinterpret_cast<uint32_t *>(dbg.validMask)[(uint64_t)rec * 4u + warp] = mask_word;
+                    int32_t *g = reinterpret_cast<int32_t *>(dbg.qkAcc) + ((uint64_t)rec * 128u + key) * 16u;
+                    *reinterpret_cast<uint4 *>(g + half * 4u) = make_uint4(s_hi[0], s_hi[1], s_hi[2], s_hi[3]);
+                    *reinterpret_cast<uint4 *>(g + 8u + half * 4u) = make_uint4(s_lo[0], s_lo[1], s_lo[2], s_lo[3]);
                 }
             }
 
-            float logit[8];
+            float logit[4];
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                const float dots = __fadd_rn((float)(int)s[h], __fmul_rn((float)(int)s[8 + h], kInv127));
-                logit[h] = valid ? __fmul_rn(dots, alphas[kind * 8u + h]) : kMasked;
+            for (int i = 0; i < 4; ++i) {
+                const float dots = __fadd_rn((float)(int)s_hi[i], __fmul_rn((float)(int)s_lo[i], kInv127));
+                logit[i] = valid ? __fmul_rn(dots, alphas[kind * 8u + half * 4u + i]) : kMasked;
             }
-            const float wmax = warp_max8(logit, lane);
-            float *slot_red = red + (gt & 1u) * 32u;
-            if ((lane & 3u) == 0) slot_red[warp * 8u + reduced_value_index(lane)] = wmax;
-            if (!group_sync(sm, 0, group_phase)) return;
-#ifdef SHAREDKV_TIMING
-            const long long t_c = clock64();
-            timing_add(36, t_c - t_b);
-#endif
+            const float wmax = warp_reduce4<true>(logit, lane);
+            float *slot_red = red + (gt & 1u) * 16u;
+            if ((lane & 7u) == 0) slot_red[warp * 4u + (lane >> 3)] = wmax;
+            if (!group_sync(sm, half, group_phase)) return;
             // rescale factors of this tile go to the accumulate warps through an 8-deep ring (the softmax
             // warps can be at most five tiles ahead of the tile being drained)
             float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (gt & 7u) * 16u;
-            int p_hi[8], p_lo[8];
+            int p_hi[4], p_lo[4];
+            float r[4];
 #pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                const float tmax = fmaxf(fmaxf(slot_red[h], slot_red[8 + h]), fmaxf(slot_red[16 + h], slot_red[24 + h]));
-                const float mnew = fmaxf(m[h], tmax);
-                const float r = expf(__fsub_rn(m[h], mnew));
-                const float w = expf(__fsub_rn(logit[h], mnew));
-                l[h] = __fadd_rn(__fmul_rn(l[h], r), w);
+            for (int i = 0; i < 4; ++i) {
+                const float tmax = fmaxf(fmaxf(slot_red[i], slot_red[4 + i]), fmaxf(slot_red[8 + i], slot_red[12 + i]));
+                const float mnew = fmaxf(m[i], tmax);
+                r[i] = expf(__fsub_rn(m[i], mnew));
+                const float w = expf(__fsub_rn(logit[i], mnew));
+                l[i] = __fadd_rn(__fmul_rn(l[i], r[i]), w);
+                // round-half-even of a value in [0, 127] without the conversion unit: adding and
+                // subtracting 1.5 * 2^23 leaves the nearest integer; its low mantissa bits are the code
                 const float w127 = __fmul_rn(w, 127.f);
-                const float hf = rintf(w127);
-                p_hi[h] = (int)hf;
-                p_lo[h] = (int)rintf(__fmul_rn(__fsub_rn(w127, hf), 127.f));
-                m[h] = mnew;
-                if (tid == 0) ring[h] = r;
+                const float shifted = __fadd_rn(w127, 12582912.f);
+                const float hf = __fsub_rn(shifted, 12582912.f);
+                p_hi[i] = (int)(__float_as_uint(shifted) - 0x4b400000u);
+                const float shifted_lo = __fadd_rn(__fmul_rn(__fsub_rn(w127, hf), 127.f), 12582912.f);
+                p_lo[i] = (int)(__float_as_uint(shifted_lo) - 0x4b400000u);
+                m[i] = mnew;
             }
-            if (tid == 0) {
-                reinterpret_cast<uint32_t *>(ring)[8] = rec;
+            if (key == 0) {
+                *reinterpret_cast<float4 *>(ring + half * 4u) = make_float4(r[0], r[1], r[2], r[3]);
+                if (half == 0) reinterpret_cast<uint32_t *>(ring)[8] = rec;
                 mbar_arrive(sm.bar(kBarRescale + (gt & 7u)));
             }
-            const uint4 codes = make_uint4(pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), pack4(p_hi[4], p_hi[5], p_hi[6], p_hi[7]),
-                                           pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]), pack4(p_lo[4], p_lo[5], p_lo[6], p_lo[7]));
-            *reinterpret_cast<uint4 *>(sm.ptr + kSmP + buf * 2048u + tid * 16u) = codes;
-            if (DEBUG && rec < dbg.maxTiles)
-                reinterpret_cast<uint4 *>(dbg.pCodes)[(uint64_t)rec * 128u + tid] = codes;
+            uint32_t *pdst = reinterpret_cast<uint32_t *>(sm.ptr + kSmP + buf * 2048u + key * 16u);
+            const uint32_t c_hi = pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), c_lo = pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]);
+            pdst[half] = c_hi;
+            pdst[2u + half] = c_lo;
+            if (DEBUG && rec < dbg.maxTiles) {
+                uint32_t *g = reinterpret_cast<uint32_t *>(dbg.pCodes) + ((uint64_t)rec * 128u + key) * 4u;
+                g[half] = c_hi;
+                g[2u + half] = c_lo;
+            }
             fence_proxy_async_smem();
             mbar_arrive(sm.bar(kBarPReady + buf));
-#ifdef SHAREDKV_TIMING
-            timing_add(37, clock64() - t_c);
-#endif
         }
 
         // denominators: sum the per-thread partial sums, hand (m, l) to the accumulate warps
         {
-            const float wsum = warp_sum8(l, lane);
-            if (!group_sync(sm, 0, group_phase)) return;   // everyone is past the last tile's reads of `red`
-            if ((lane & 3u) == 0) red[warp * 8u + reduced_value_index(lane)] = wsum;
-            if (!group_sync(sm, 0, group_phase)) return;
-            if (tid == 0) {
+            const float wsum = warp_reduce4<false>(l, lane);
+            if (!group_sync(sm, half, group_phase)) return;   // everyone is past the last tile's reads of `red`
+            if ((lane & 7u) == 0) red[warp * 4u + (lane >> 3)] = wsum;
+            if (!group_sync(sm, half, group_phase)) return;
+            if (key == 0) {
                 float *fin = reinterpret_cast<float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
 #pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    fin[h] = m[h];
-                    fin[8 + h] = __fadd_rn(__fadd_rn(red[h], red[8 + h]), __fadd_rn(red[16 + h], red[24 + h]));
+                for (int i = 0; i < 4; ++i) {
+                    fin[half * 4u + i] = m[i];
+                    fin[8u + half * 4u + i] = __fadd_rn(__fadd_rn(red[i], red[4 + i]), __fadd_rn(red[8 + i], red[12 + i]));
                 }
                 mbar_arrive(sm.bar(kBarItemDone + (k & 7u)));
             }
@@ -912,16 +980,25 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
     }
 }
 
-// ------------------------------------------------------------------ accumulate warps (4-7)
-// Thread = one channel of each of the four 128-channel blocks, all eight heads.  Drains the
-// INT32 PV accumulators of every tile into FP32 running sums, then normalises and stores the
-// token (or its partial state, merging when this CTA holds the last piece to arrive).
+// ------------------------------------------------------------------ accumulate warps (8-11)
+// Thread = channel c of each of the four 128-channel blocks, all eight heads.  Drains the INT32
+// PV accumulators of every tile into FP32 running sums, then normalises and stores the token (or
+// its partial state, merging when this CTA holds the last piece to arrive).
+
+// Exact FP32 value of an integer of magnitude below 2^22 without the conversion unit: adding the
+// integer to the bit pattern of 1.5 * 2^23 yields the float 1.5 * 2^23 + x, from which the
+// constant is subtracted exactly.  |PV accumulator| <= 127 * 127 * 128 < 2^21.
+__device__ __forceinline__ float small_int_to_float(uint32_t x)
+{
+    return __fsub_rn(__uint_as_float(x + 0x4b400000u), 12582912.f);
+}
+
 template <int RATIO, bool DEBUG>
 __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const PlanHeader *header,
                                 const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
-    const uint32_t tid = threadIdx.x - 128u;       // 0..127
-    const uint32_t warp = tid >> 5;
+    const uint32_t ch = threadIdx.x - 256u;        // 0..127
+    const uint32_t warp = ch >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
     char *ws = reinterpret_cast<char *>(p.workspace);
     uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
@@ -934,15 +1011,15 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
     for (int kind = 0; kind < 2; ++kind)
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + tid];
+        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + ch];
 
     // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
     {
         const uint32_t live = header->live_tokens;
         for (uint32_t t = live + blockIdx.x; t < p.tokens; t += gridDim.x) {
             uint4 *o = reinterpret_cast<uint4 *>(p.out) + (uint64_t)t * 512u;
-            for (uint32_t i = tid; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
-            if (p.lse && tid < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)t * 8u + tid] = 0.f;
+            for (uint32_t i = ch; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
+            if (p.lse && ch < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)t * 8u + ch] = 0.f;
         }
     }
 
@@ -953,39 +1030,44 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         const Item it = cur.it;
         float acc[4][8];
 #pragma unroll
-        for (int h = 0; h < 8; ++h)
+        for (int mb = 0; mb < 4; ++mb)
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
+            for (int h = 0; h < 8; ++h) acc[mb][h] = 0.f;
 
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
             const uint32_t buf = gt & 1u, ph = (gt >> 1) & 1u, slot = gt & 7u;
             if (!wait_phase(sm, kBarRescale + slot, (gt >> 3) & 1u)) return;
-            const float *ring = reinterpret_cast<const float *>(sm.ptr + kSmRescale) + slot * 16u;
-            float r[8];
-#pragma unroll
-            for (int h = 0; h < 8; ++h) r[h] = ring[h];
+            const float4 *ring = reinterpret_cast<const float4 *>(sm.ptr + kSmRescale + slot * 64u);
+            const float4 ra = ring[0], rb = ring[1];
+            const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
             const uint32_t rec = DEBUG ? reinterpret_cast<const uint32_t *>(ring)[8] : 0u;
             if (!wait_phase(sm, kBarOFull + buf, ph)) return;
             tc_fence_after();
-            uint32_t o[4][16];
 #pragma unroll
-            for (uint32_t mb = 0; mb < 4; ++mb) tmem_ld16(tmem_lane + kColO + buf * 64u + mb * 16u, o[mb]);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(sm.bar(kBarOFree + buf));
-#pragma unroll
-            for (uint32_t mb = 0; mb < 4; ++mb) {
-                if (DEBUG && rec < dbg.maxTiles) {
-                    uint4 *g = reinterpret_cast<uint4 *>(dbg.pvAcc) + ((uint64_t)rec * 512u + mb * 128u + tid) * 4u;
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[mb][4 * i], o[mb][4 * i + 1], o[mb][4 * i + 2], o[mb][4 * i + 3]);
+            for (uint32_t half = 0; half < 2; ++half) {        // two channel blocks at a time keeps registers in budget
+                uint32_t o[2][16];
+                tmem_ld16(tmem_lane + kColO + buf * 64u + (2u * half) * 16u, o[0]);
+                tmem_ld16(tmem_lane + kColO + buf * 64u + (2u * half + 1u) * 16u, o[1]);
+                tmem_wait_ld();
+                if (half == 1) {
+                    tc_fence_before();
+                    mbar_arrive(sm.bar(kBarOFree + buf));
                 }
-                const float s = j == 0 ? sc[0][mb] : sc[1][mb];
 #pragma unroll
-                for (int h = 0; h < 8; ++h) {
-                    const float dots = __fadd_rn((float)(int)o[mb][h], __fmul_rn((float)(int)o[mb][8 + h], kInv127));
-                    const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
-                    acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r[h]), pv);
+                for (uint32_t q = 0; q < 2; ++q) {
+                    const uint32_t mb = 2u * half + q;
+                    if (DEBUG && rec < dbg.maxTiles) {
+                        uint4 *g = reinterpret_cast<uint4 *>(dbg.pvAcc) + ((uint64_t)rec * 512u + mb * 128u + ch) * 4u;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[q][4 * i], o[q][4 * i + 1], o[q][4 * i + 2], o[q][4 * i + 3]);
+                    }
+                    const float s = j == 0 ? sc[0][mb] : sc[1][mb];
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) {
+                        const float dots = __fadd_rn(small_int_to_float(o[q][h]), __fmul_rn(small_int_to_float(o[q][8 + h]), kInv127));
+                        const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
+                        acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r[h]), pv);
+                    }
                 }
             }
         }
@@ -993,20 +1075,18 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         // final (m, l) of this item from the softmax warps
         if (!wait_phase(sm, kBarItemDone + (k & 7u), (k >> 3) & 1u)) return;
         const float *fin = reinterpret_cast<const float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
-        float m[8], l[8];
-#pragma unroll
-        for (int h = 0; h < 8; ++h) { m[h] = fin[h]; l[h] = fin[8 + h]; }
 
         __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.out) + (uint64_t)it.token * 4096u;
         float *lse = p.lse ? reinterpret_cast<float *>(p.lse) + (uint64_t)it.token * 8u : nullptr;
         if (it.nparts == 1) {
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
+                const float l = fin[8 + h];
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb)
-                    out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], l[h]));
+                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], l));
             }
-            if (lse && tid < 8) lse[tid] = __fadd_rn(fin[tid], logf(fin[8 + tid]));
+            if (lse && ch < 8) lse[ch] = __fadd_rn(fin[ch], logf(fin[8 + ch]));
             cursor_next_item(cur, items);
             continue;
         }
@@ -1017,30 +1097,30 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
         for (int h = 0; h < 8; ++h)
 #pragma unroll
-            for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + tid] = acc[mb][h];
-        if (tid < 16) mine[4096 + tid] = fin[tid];
+            for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + ch] = acc[mb][h];
+        if (ch < 16) mine[4096 + ch] = fin[ch];
         __threadfence();
-        if (!group_sync(sm, 1, group_phase)) return;
-        if (tid == 0) misc[3] = atomicAdd(tickets + it.token, 1u);
-        if (!group_sync(sm, 1, group_phase)) return;
+        if (!group_sync(sm, 3, group_phase)) return;
+        if (ch == 0) misc[3] = atomicAdd(tickets + it.token, 1u);
+        if (!group_sync(sm, 3, group_phase)) return;
         const uint32_t ticket = misc[3];
         if (ticket + 1u == it.nparts) {
             __threadfence();
             float top[8], den[8];
 #pragma unroll
             for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
-            for (uint32_t j = 0; j < it.nparts; ++j) {
-                const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+            for (uint32_t q = 0; q < it.nparts; ++q) {
+                const uint32_t sl = q == 0 ? it.first_cta * 2u + 1u : (it.first_cta + q) * 2u;
                 const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
             }
 #pragma unroll
-            for (int h = 0; h < 8; ++h)
+            for (int mb = 0; mb < 4; ++mb)
 #pragma unroll
-                for (int mb = 0; mb < 4; ++mb) acc[mb][h] = 0.f;
-            for (uint32_t j = 0; j < it.nparts; ++j) {
-                const uint32_t sl = j == 0 ? it.first_cta * 2u + 1u : (it.first_cta + j) * 2u;
+                for (int h = 0; h < 8; ++h) acc[mb][h] = 0.f;
+            for (uint32_t q = 0; q < it.nparts; ++q) {
+                const uint32_t sl = q == 0 ? it.first_cta * 2u + 1u : (it.first_cta + q) * 2u;
                 const float *ps = partials + (uint64_t)sl * kPartialFloats;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
@@ -1048,19 +1128,19 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
                     den[h] = __fadd_rn(den[h], __fmul_rn(__ldcg(ps + 4104 + h), g));
 #pragma unroll
                     for (int mb = 0; mb < 4; ++mb)
-                        acc[mb][h] = __fadd_rn(acc[mb][h], __fmul_rn(__ldcg(ps + h * 512 + mb * 128 + tid), g));
+                        acc[mb][h] = __fadd_rn(acc[mb][h], __fmul_rn(__ldcg(ps + h * 512 + mb * 128 + ch), g));
                 }
             }
 #pragma unroll
             for (int h = 0; h < 8; ++h)
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb)
-                    out[h * 512 + mb * 128 + tid] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
-            if (lse && tid < 8) {
+                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
+            if (lse && ch < 8) {
                 float mm = top[0], ll = den[0];
 #pragma unroll
-                for (int h = 1; h < 8; ++h) if (tid == (uint32_t)h) { mm = top[h]; ll = den[h]; }
-                lse[tid] = __fadd_rn(mm, logf(ll));
+                for (int h = 1; h < 8; ++h) if (ch == (uint32_t)h) { mm = top[h]; ll = den[h]; }
+                lse[ch] = __fadd_rn(mm, logf(ll));
             }
         }
         cursor_next_item(cur, items);
@@ -1071,7 +1151,8 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 template <int RATIO, bool DEBUG, bool TMA>
 __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs p, const SharedKVDebug dbg,
                                                              const __grid_constant__ CUtensorMap ori_map,
-                                                             const __grid_constant__ CUtensorMap cmp_map)
+                                                             const __grid_constant__ CUtensorMap cmp_map,
+                                                             const __grid_constant__ CUtensorMap cmp_page_map)
 {
     extern __shared__ char smem_raw[];
     Shared sm;
@@ -1087,16 +1168,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) { mbar_init(sm.bar(kBarFull + s), TMA ? 4 : 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
         for (uint32_t b = 0; b < 2; ++b) {
-            mbar_init(sm.bar(kBarSFull + b), 1); mbar_init(sm.bar(kBarSFree + b), 128);
-            mbar_init(sm.bar(kBarPReady + b), 128); mbar_init(sm.bar(kBarOFull + b), 1); mbar_init(sm.bar(kBarOFree + b), 128);
-            mbar_init(sm.bar(kBarGroup + b), 128);
+            mbar_init(sm.bar(kBarSFull + b), 1); mbar_init(sm.bar(kBarSFree + b), 256);
+            mbar_init(sm.bar(kBarPReady + b), 256); mbar_init(sm.bar(kBarOFull + b), 1); mbar_init(sm.bar(kBarOFree + b), 128);
+            mbar_init(sm.bar(kBarGroup + b), 128);          // one per softmax half
+            mbar_init(sm.bar(kBarGroup + 2 + b), b == 0 ? 256 : 128);      // all softmax threads; all accumulate threads
         }
-        mbar_init(sm.bar(kBarQReady), 128);
-        for (uint32_t i = 0; i < 8; ++i) { mbar_init(sm.bar(kBarRescale + i), 1); mbar_init(sm.bar(kBarItemDone + i), 1); }
+        mbar_init(sm.bar(kBarQReady), 256);
+        for (uint32_t i = 0; i < 8; ++i) { mbar_init(sm.bar(kBarRescale + i), 2); mbar_init(sm.bar(kBarItemDone + i), 2); }
         misc[1] = 0; misc[2] = 0; misc[3] = 0;
         fence_mbar_init();
     }
-    if (warp == 12) {
+    if (warp == kWarpMma) {
         tmem_alloc(sm.base + kSmMisc, kTmemCols);
         tmem_relinquish();
     }
@@ -1119,13 +1201,16 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
     const uint32_t first = cta_first[blockIdx.x], end = cta_first[blockIdx.x + 1];
 
-    if (warp < 4) {
+    if (warp < 8) {
         softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, first, end, tmem);
-    } else if (warp < 8) {
+    } else if (warp < kWarpProducer) {
         accumulate_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
-    } else if (warp < 12) {
-        if (TMA && lane == 0) { tma_prefetch_descriptor(&ori_map); tma_prefetch_descriptor(&cmp_map); }
-        producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - 8u, lane, &ori_map, &cmp_map);
+    } else if (warp < kWarpMma) {
+        if (TMA && lane == 0) {
+            tma_prefetch_descriptor(&ori_map);
+            tma_prefetch_descriptor(RATIO == 128 ? &cmp_page_map : &cmp_map);
+        }
+        producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - kWarpProducer, lane, &ori_map, &cmp_map, &cmp_page_map);
         cp_async_wait<0>();
     } else {
         if (lane == 0) mma_loop(sm, items, first, end, tmem);
@@ -1138,7 +1223,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     __syncthreads();
     if (tid == 0 && misc[1])
         reinterpret_cast<PlanHeader *>(const_cast<char *>(ws))->status = kStatusWaitTimeout;
-    if (warp == 12) {
+    if (warp == kWarpMma) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
@@ -1177,9 +1262,25 @@ bool make_row_map(CUtensorMap *map, uint64_t base)
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D view of a paged cache for whole-page fetches: [pages, 32 rows, 512 bytes]; box = one page's
+// 128-byte column block (4 KB).
+bool make_page_map(CUtensorMap *map, uint64_t base, uint64_t page_stride)
+{
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {kDim, kPage, (cuuint64_t)1 << 31};
+    const cuuint64_t strides[2] = {kDim, page_stride};
+    const cuuint32_t box[3] = {128, kPage, 1};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, reinterpret_cast<void *>(base), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int RATIO, bool DEBUG, bool TMA>
 cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const CUtensorMap &ori_map,
-                          const CUtensorMap &cmp_map, uint32_t grid, cudaStream_t stream, int device)
+                          const CUtensorMap &cmp_map, const CUtensorMap &cmp_page_map, uint32_t grid,
+                          cudaStream_t stream, int device)
 {
     // the opt-in to > 48 KB of dynamic shared memory is per device and per kernel
     static std::atomic<uint64_t> configured{0};
@@ -1190,7 +1291,7 @@ cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const C
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_relaxed);
     }
-    decode_kernel<RATIO, DEBUG, TMA><<<grid, kThreads, kSmemBytes, stream>>>(a, d, ori_map, cmp_map);
+    decode_kernel<RATIO, DEBUG, TMA><<<grid, kThreads, kSmemBytes, stream>>>(a, d, ori_map, cmp_map, cmp_page_map);
     return cudaGetLastError();
 }
 
@@ -1205,10 +1306,12 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
     if (e != cudaSuccess) return (int)e;
     // Row gathers by TMA need page strides that are whole rows and row ids that fit the map;
     // anything else takes the cp.async producer.
-    CUtensorMap ori_map, cmp_map;
+    CUtensorMap ori_map, cmp_map, cmp_page_map;
     bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 && !(debug && (debug->reserved & 0x80000000u)) &&
                (uint64_t)a.oriPages * (a.oriStride / kDim) < (uint64_t)kRowsInMap && a.cmpStride / kDim < 65536;
-    if (tma) tma = make_row_map(&ori_map, a.ori) && make_row_map(&cmp_map, a.cmp);
+    memset(&cmp_page_map, 0, sizeof(cmp_page_map));
+    if (tma) tma = make_row_map(&ori_map, a.ori) && make_row_map(&cmp_map, a.cmp) &&
+                   (RATIO != 128 || make_page_map(&cmp_page_map, a.cmp, a.cmpStride));
     if (!tma) { memset(&ori_map, 0, sizeof(ori_map)); memset(&cmp_map, 0, sizeof(cmp_map)); }
     plan_kernel<RATIO><<<1, kPlanThreads, 0, stream>>>(a, grid);
     e = cudaGetLastError();
@@ -1216,11 +1319,11 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
     SharedKVDebug d = {};
     if (debug) {
         d = *debug;
-        e = tma ? launch_decode<RATIO, true, true>(a, d, ori_map, cmp_map, grid, stream, device)
-                : launch_decode<RATIO, true, false>(a, d, ori_map, cmp_map, grid, stream, device);
+        e = tma ? launch_decode<RATIO, true, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+                : launch_decode<RATIO, true, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
     } else {
-        e = tma ? launch_decode<RATIO, false, true>(a, d, ori_map, cmp_map, grid, stream, device)
-                : launch_decode<RATIO, false, false>(a, d, ori_map, cmp_map, grid, stream, device);
+        e = tma ? launch_decode<RATIO, false, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+                : launch_decode<RATIO, false, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
     }
     return (int)e;
 }
@@ -1232,7 +1335,7 @@ extern "C" __attribute__((visibility("default"))) int sharedkv_timing_read(unsig
 {
     cudaError_t e = cudaMemcpyFromSymbol(host, g_wait_cycles, sizeof(g_wait_cycles));
     if (e == cudaSuccess && reset) {
-        static unsigned long long zeros[kMaxCtas][160];
+        static unsigned long long zeros[kMaxCtas][240];
         e = cudaMemcpyToSymbol(g_wait_cycles, zeros, sizeof(zeros));
     }
     return (int)e;

@@ -72,6 +72,15 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const void *tensor_map
         ::"r"(dst), "l"(tensor_map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar)
         : "memory");
 }
+// One box {128 bytes, 32 rows, 1 page} of a 3-D [512 B, 32 rows, pages] view: a whole page's
+// 128-channel segment (4 KB) per instruction.
+__device__ __forceinline__ void tma_page_segment(uint32_t dst, const void *tensor_map, int32_t x, int32_t page, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(tensor_map), "r"(x), "r"(0), "r"(page), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_descriptor(const void *tensor_map)
 {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
@@ -118,6 +127,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
 }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc], INT8 x INT8 -> INT32, one CTA.
