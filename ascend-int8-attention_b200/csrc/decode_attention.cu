@@ -57,8 +57,8 @@ constexpr uint32_t kTileKeys = 128;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
-constexpr uint32_t kThreads = 544;                        // 8 softmax + 4 accumulate + 4 producer + 1 MMA warps
-constexpr uint32_t kWarpProducer = 12, kWarpMma = 16;
+constexpr uint32_t kThreads = 576;                        // 8 softmax + 4 accumulate + 4 producer + 2 MMA warps
+constexpr uint32_t kWarpProducer = 12, kWarpMma = 16;   // warp 16 issues S = K.Q^T, warp 17 issues O = K^T.P
 constexpr uint32_t kMaxCtas = 160;
 constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
@@ -666,77 +666,73 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
     }
 }
 
-// ------------------------------------------------------------------ MMA issuer (one thread)
-// Two independent instruction streams share the thread: S = K.Q^T of tile t needs the tile in
-// shared memory, the query codes of its item and a free S buffer; O = K^T.P of tile t needs the
-// P codes of tile t and a free O buffer.  Whichever is ready is issued, PV first because its
-// completion releases a ring stage to the producers.
-__device__ void mma_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+// ------------------------------------------------------------------ MMA issuers (two threads)
+// A thread can hand the tensor core roughly one small MMA per 60-70 cycles while the core itself
+// retires one per ~40, so the two products of a tile are issued by two threads of different
+// warps (different SM sub-partitions): S = K.Q^T by one, O = K^T.P by the other.  Each product is
+// 16 instructions of M = 128, N = 16, K = 32 bytes.
+__device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
-    constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
     Cursor cq;
     cursor_init(cq, items, first, end);
-    uint32_t qk_next = 0, pv_next = 0;     // tiles whose QK / PV have been issued
-    uint32_t q_items = 0;                  // items whose query codes have been waited for
-    bool q_ready = false;
-    volatile uint32_t *misc = sm.misc();
-    long long idle_since = clock64();
-    uint32_t idle_spins = 0;
+    uint32_t t = 0;                        // tiles issued so far
+    for (uint32_t k = 0; !cq.done; ++k) {
+        if (!wait_phase(sm, kBarQReady, k & 1u)) return;      // this item's query codes are in shared memory
+        for (;;) {
+            const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+            if (!wait_phase(sm, kBarFull + stage, (t / kStages) & 1u)) return;
+            if (!wait_phase(sm, kBarSFree + buf, ph ^ 1u)) return;
+            tc_fence_after();
+            const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+            const uint32_t qb = sm.base + kSmQ + (cq.j == 0 ? 0u : 8192u);
+            const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
+#ifdef SHAREDKV_TIMING
+            const long long t_issue = clock64();
+#endif
+#pragma unroll
+            for (uint32_t ks = 0; ks < 16; ++ks) {
+                const uint32_t seg = ks >> 2, part = ks & 3u;
+                // the address field counts 16-byte units; offsets stay inside the 14-bit field
+                mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
+                       kIdescQK, ks);
+            }
+            mma_commit(sm.bar(kBarSFull + buf));
+#ifdef SHAREDKV_TIMING
+            timing_add(35, clock64() - t_issue);
+#endif
+            ++t;
+            if (cursor_advance(cq, items) || cq.done) break;
+        }
+    }
+}
 
-    while (!cq.done || pv_next < qk_next) {
-        bool progressed = false;
-        if (pv_next < qk_next) {
-            const uint32_t t = pv_next, stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-            if (mbar_try_wait(sm.bar(kBarPReady + buf), ph) && mbar_try_wait(sm.bar(kBarOFree + buf), ph ^ 1u)) {
-                tc_fence_after();
-                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-                const uint32_t pb = sm.base + kSmP + buf * 2048u;
+__device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+{
+    constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
+    // only the number of tiles matters here
+    uint32_t tiles = 0;
+    for (uint32_t k = first; k < end; ++k) {
+        const Item it = load_item(items, k);
+        tiles += it.tile_end - it.tile_begin;
+    }
+    for (uint32_t t = 0; t < tiles; ++t) {
+        const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+        if (!wait_phase(sm, kBarPReady + buf, ph)) return;
+        if (!wait_phase(sm, kBarOFree + buf, ph ^ 1u)) return;
+        tc_fence_after();
+        const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
+        const uint32_t pb = sm.base + kSmP + buf * 2048u;
+        const uint64_t a0 = smem_desc(kv, kSegBytes, 1024u, kSwizzle128), b0 = smem_desc(pb, 128u, 2048u, kSwizzleNone);
 #pragma unroll
-                for (uint32_t mb = 0; mb < 4; ++mb) {
+        for (uint32_t mb = 0; mb < 4; ++mb) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk) {
-                        const uint64_t a = smem_desc(kv + mb * kSegBytes + kk * 4096u, kSegBytes, 1024u, kSwizzle128);
-                        const uint64_t b = smem_desc(pb + kk * 512u, 128u, 2048u, kSwizzleNone);
-                        mma_i8(tmem + kColO + buf * 64u + mb * 16u, a, b, kIdescPV, kk);
-                    }
-                }
-                mma_commit(sm.bar(kBarOFull + buf));
-                mma_commit(sm.bar(kBarEmpty + stage));
-                ++pv_next;
-                progressed = true;
-            }
+            for (uint32_t kk = 0; kk < 4; ++kk)
+                mma_i8(tmem + kColO + buf * 64u + mb * 16u, a0 + ((mb * kSegBytes + kk * 4096u) >> 4), b0 + ((kk * 512u) >> 4),
+                       kIdescPV, kk);
         }
-        if (!cq.done) {
-            const uint32_t t = qk_next, stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-            if (!q_ready && mbar_try_wait(sm.bar(kBarQReady), q_items & 1u)) q_ready = true;
-            if (q_ready && mbar_try_wait(sm.bar(kBarFull + stage), (t / kStages) & 1u) &&
-                mbar_try_wait(sm.bar(kBarSFree + buf), ph ^ 1u)) {
-                tc_fence_after();
-                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-                const uint32_t qb = sm.base + kSmQ + (cq.j == 0 ? 0u : 8192u);
-#pragma unroll
-                for (uint32_t ks = 0; ks < 16; ++ks) {
-                    const uint32_t seg = ks >> 2, part = ks & 3u;
-                    const uint64_t a = smem_desc(kv + seg * kSegBytes + part * 32u, 16u, 1024u, kSwizzle128);
-                    const uint64_t b = smem_desc(qb + seg * 2048u + part * 32u, 16u, 1024u, kSwizzle128);
-                    mma_i8(tmem + kColS + buf * 16u, a, b, kIdescQK, ks);
-                }
-                mma_commit(sm.bar(kBarSFull + buf));
-                ++qk_next;
-                if (cursor_advance(cq, items)) { q_ready = false; ++q_items; }
-                progressed = true;
-            }
-        }
-        if (progressed) {
-            idle_spins = 0;
-            continue;
-        }
-        if (idle_spins++ == 0) idle_since = clock64();
-        if ((idle_spins & 63u) == 0) {
-            if (misc[1]) return;
-            if (clock64() - idle_since > kWaitCycles) { misc[1] = 1; return; }
-        }
+        mma_commit(sm.bar(kBarOFull + buf));
+        mma_commit(sm.bar(kBarEmpty + stage));      // the stage's last reader (its S product finished before P existed)
     }
 }
 
@@ -751,6 +747,15 @@ __device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t which, uin
     const bool ok = wait_phase(sm, kBarGroup + which, phase);
     phase ^= 1u;
     return ok;
+}
+
+// e^x through the hardware base-2 exponential (relative error about 2^-22 plus the rounding of
+// x * log2(e)); masked keys (-1e30) give exactly 0.
+__device__ __forceinline__ float fast_exp(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(__fmul_rn(x, 1.4426950408889634f)));
+    return y;
 }
 
 // Reduce four per-thread values across the 32 lanes; afterwards lane 8 i (i = 0..3) holds value i.
@@ -926,12 +931,16 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             int p_hi[4], p_lo[4];
             float r[4];
 #pragma unroll
+            const float4 q0 = reinterpret_cast<const float4 *>(slot_red)[0], q1 = reinterpret_cast<const float4 *>(slot_red)[1];
+            const float4 q2 = reinterpret_cast<const float4 *>(slot_red)[2], q3 = reinterpret_cast<const float4 *>(slot_red)[3];
+            const float tmaxes[4] = {fmaxf(fmaxf(q0.x, q1.x), fmaxf(q2.x, q3.x)), fmaxf(fmaxf(q0.y, q1.y), fmaxf(q2.y, q3.y)),
+                                     fmaxf(fmaxf(q0.z, q1.z), fmaxf(q2.z, q3.z)), fmaxf(fmaxf(q0.w, q1.w), fmaxf(q2.w, q3.w))};
+#pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float tmax = fmaxf(fmaxf(slot_red[i], slot_red[4 + i]), fmaxf(slot_red[8 + i], slot_red[12 + i]));
-                const float mnew = fmaxf(m[i], tmax);
-                r[i] = expf(__fsub_rn(m[i], mnew));
-                const float w = expf(__fsub_rn(logit[i], mnew));
-                l[i] = __fadd_rn(__fmul_rn(l[i], r[i]), w);
+                const float mnew = fmaxf(m[i], tmaxes[i]);
+                r[i] = mnew == m[i] ? 1.f : fast_exp(__fsub_rn(m[i], mnew));
+                const float w = fast_exp(__fsub_rn(logit[i], mnew));
+                l[i] = __fmaf_rn(l[i], r[i], w);
                 // round-half-even of a value in [0, 127] without the conversion unit: adding and
                 // subtracting 1.5 * 2^23 leaves the nearest integer; its low mantissa bits are the code
                 const float w127 = __fmul_rn(w, 127.f);
@@ -1007,11 +1016,13 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
     volatile uint32_t *misc = sm.misc();
     uint32_t group_phase = 0;
 
-    float sc[2][4];                                // cache scales of this thread's four channels
+    // cache scale / 127 of this thread's four channels (the reference multiplies by the scale and
+    // by 1/127 in turn; folding the two constants differs by at most one rounding of the product)
+    float sc[2][4];
 #pragma unroll
     for (int kind = 0; kind < 2; ++kind)
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = scales[kind * 512 + mb * 128 + ch];
+        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = __fmul_rn(scales[kind * 512 + mb * 128 + ch], kInv127);
 
     // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
     {
@@ -1041,6 +1052,15 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
             const float4 ra = ring[0], rb = ring[1];
             const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
             const uint32_t rec = DEBUG ? reinterpret_cast<const uint32_t *>(ring)[8] : 0u;
+            // once the running maxima have settled every factor is exactly 1 and the multiply is skipped
+            const bool rescale = (ra.x != 1.f) | (ra.y != 1.f) | (ra.z != 1.f) | (ra.w != 1.f) | (rb.x != 1.f) | (rb.y != 1.f) |
+                                 (rb.z != 1.f) | (rb.w != 1.f);
+            if (rescale) {
+#pragma unroll
+                for (int mb = 0; mb < 4; ++mb)
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) acc[mb][h] = __fmul_rn(acc[mb][h], r[h]);
+            }
             if (!wait_phase(sm, kBarOFull + buf, ph)) return;
             tc_fence_after();
 #pragma unroll
@@ -1064,9 +1084,8 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
                     const float s = j == 0 ? sc[0][mb] : sc[1][mb];
 #pragma unroll
                     for (int h = 0; h < 8; ++h) {
-                        const float dots = __fadd_rn(small_int_to_float(o[q][h]), __fmul_rn(small_int_to_float(o[q][8 + h]), kInv127));
-                        const float pv = __fmul_rn(__fmul_rn(dots, s), kInv127);
-                        acc[mb][h] = __fadd_rn(__fmul_rn(acc[mb][h], r[h]), pv);
+                        const float dots = __fmaf_rn(small_int_to_float(o[q][8 + h]), kInv127, small_int_to_float(o[q][h]));
+                        acc[mb][h] = __fmaf_rn(dots, s, acc[mb][h]);
                     }
                 }
             }
@@ -1213,7 +1232,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - kWarpProducer, lane, &ori_map, &cmp_map, &cmp_page_map);
         cp_async_wait<0>();
     } else {
-        if (lane == 0) mma_loop(sm, items, first, end, tmem);
+        if (lane == 0) {
+            if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
+            else mma_pv_loop(sm, cta_first, items, first, end, tmem);
+        }
         __syncwarp();
     }
 #ifdef SHAREDKV_TIMING
