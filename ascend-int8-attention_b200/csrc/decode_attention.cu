@@ -57,8 +57,9 @@ constexpr uint32_t kTileKeys = 128;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
-constexpr uint32_t kThreads = 576;                        // 8 softmax + 4 accumulate + 4 producer + 2 MMA warps
+constexpr uint32_t kThreads = 640;                        // 8 softmax + 4 accumulate + 4 producer + 2 MMA + 2 query warps
 constexpr uint32_t kWarpProducer = 12, kWarpMma = 16;   // warp 16 issues S = K.Q^T, warp 17 issues O = K^T.P
+constexpr uint32_t kWarpQuery = 18;                      // warps 18 / 19 encode the query for the original / compressed scales
 constexpr uint32_t kMaxCtas = 160;
 constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
@@ -68,19 +69,21 @@ constexpr long long kWaitCycles = 4000000000ll;              // ~2 s: a wait tha
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kSmKv = 0;
-constexpr uint32_t kSmQ = kSmKv + kStages * kTileBytes;      // 2 kinds x 16 rows x 512 B, swizzled
-constexpr uint32_t kSmP = kSmQ + 2 * 8192;                   // 2 buffers x 128 keys x 16 B
-constexpr uint32_t kSmScale = kSmP + 2 * 2048;               // FP32 [2][512]
-constexpr uint32_t kSmMask = kSmScale + 2 * 2048;            // UINT32 [stages][4]: bit k of the 128-bit word = slot k holds a key
+constexpr uint32_t kSmQ = kSmKv + kStages * kTileBytes;      // query codes, 16 rows x 512 B swizzled: original kind, then
+                                                             // two buffers of the compressed kind (alternating items)
+constexpr uint32_t kSmP = kSmQ + 3 * 8192;                   // 2 buffers x 128 keys x 16 B
+constexpr uint32_t kSmMask = kSmP + 2 * 2048;                // UINT32 [stages][4]: bit k of the 128-bit word = slot k holds a key
 constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2 halves][2 parities][4 warps][4]
-constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [2 kinds][8]: alpha * softmax_scale
-constexpr uint32_t kSmRescale = kSmAlpha + 64;               // [8 tiles][16]: r[8], debug record, pad
+constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [8 items][2 kinds][8]: alpha * softmax_scale
+constexpr uint32_t kSmRescale = kSmAlpha + 8 * 64;              // [8 tiles][16]: r[8], debug record, pad
 constexpr uint32_t kSmFinal = kSmRescale + 8 * 64;           // [8 items][16]: m[8], l[8]
-constexpr uint32_t kSmItems = kSmFinal + 8 * 64;             // producers: per warp a ring of 16 decoded work items
-constexpr uint32_t kSmBar = kSmItems + 4 * 16 * 32;          // mbarriers
+constexpr uint32_t kSmItems = kSmFinal + 8 * 64;             // producers: per warp a ring of 16 work items (16 B each)
+constexpr uint32_t kSmRowIds = kSmItems + 4 * 16 * 16;       // producers: per warp [lookahead][32 lanes] row ids
+constexpr uint32_t kSmBar = kSmRowIds + 4 * 2 * 32 * 4;      // mbarriers
 constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kBarPReady = 10, kBarOFull = 12,
-                   kBarOFree = 14, kBarQReady = 16, kBarGroup = 17 /* x4: softmax halves, all softmax, all accumulate */,
-                   kBarRescale = 21 /* x8 */, kBarItemDone = 29 /* x8 */, kNumBars = 37;
+                   kBarOFree = 14, kBarQReady = 16 /* x3 query buffers */, kBarQFree = 19 /* x3 */,
+                   kBarGroup = 22 /* x4: softmax halves, all softmax, all accumulate */,
+                   kBarRescale = 26 /* x8 */, kBarItemDone = 34 /* x8 */, kNumBars = 42;
 constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words
 constexpr uint32_t kSmemBytes = kSmMisc + 16 + 1024;         // + alignment slack
 static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
@@ -279,15 +282,11 @@ __device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
 }
 #endif
 
-// Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.
-__device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
+// Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.  The common case, a
+// phase that is already complete, is one instruction inline; the polling loop lives out of line so
+// that the many call sites stay small (the kernel's hot loops have to share the instruction cache).
+__device__ __noinline__ bool wait_phase_slow(uint32_t bar, uint32_t parity, volatile uint32_t *misc)
 {
-    const uint32_t bar = sm.bar(bar_index);
-#ifdef SHAREDKV_TIMING
-    struct Scope { uint32_t i; long long t0; __device__ ~Scope() { timing_add(i, clock64() - t0); } } scope{bar_index, clock64()};
-#endif
-    if (mbar_try_wait(bar, parity)) return true;
-    volatile uint32_t *misc = sm.misc();
     const long long start = clock64();
 #pragma unroll 1
     for (uint32_t spin = 1;; ++spin) {
@@ -297,6 +296,15 @@ __device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index,
             if (clock64() - start > kWaitCycles) { misc[1] = 1; return false; }
         }
     }
+}
+__device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
+{
+    const uint32_t bar = sm.bar(bar_index);
+#ifdef SHAREDKV_TIMING
+    struct Scope { uint32_t i; long long t0; __device__ ~Scope() { timing_add(i, clock64() - t0); } } scope{bar_index, clock64()};
+#endif
+    if (mbar_try_wait(bar, parity)) return true;
+    return wait_phase_slow(bar, parity, sm.misc());
 }
 
 __device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
@@ -317,56 +325,6 @@ __device__ __forceinline__ uint32_t tile_offset(uint32_t row, uint32_t chunk, ui
     return seg * seg_bytes + (row >> 3) * 1024u + r * 128u + ((c ^ r) << 4);
 }
 
-// Reduce eight per-thread values across the 32 lanes with max; afterwards lane 4 h (h = 0..7)
-// holds the warp-wide maximum of value h.  9 shuffles instead of 40.
-__device__ __forceinline__ float warp_max8(const float (&v)[8], uint32_t lane)
-{
-    float a[4], b[2], c;
-    const bool up16 = lane & 16u, up8 = lane & 8u, up4 = lane & 4u;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float send = up16 ? v[i] : v[i + 4], keep = up16 ? v[i + 4] : v[i];
-        a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 16));
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const float send = up8 ? a[i] : a[i + 2], keep = up8 ? a[i + 2] : a[i];
-        b[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 8));
-    }
-    {
-        const float send = up4 ? b[0] : b[1], keep = up4 ? b[1] : b[0];
-        c = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 4));
-    }
-    c = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, 2));
-    c = fmaxf(c, __shfl_xor_sync(0xffffffffu, c, 1));
-    return c;   // value index = 4*bit4 + 2*bit3 + bit2 of the lane
-}
-__device__ __forceinline__ float warp_sum8(const float (&v)[8], uint32_t lane)
-{
-    float a[4], b[2], c;
-    const bool up16 = lane & 16u, up8 = lane & 8u, up4 = lane & 4u;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float send = up16 ? v[i] : v[i + 4], keep = up16 ? v[i + 4] : v[i];
-        a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const float send = up8 ? a[i] : a[i + 2], keep = up8 ? a[i + 2] : a[i];
-        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-    {
-        const float send = up4 ? b[0] : b[1], keep = up4 ? b[1] : b[0];
-        c = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    c += __shfl_xor_sync(0xffffffffu, c, 2);
-    c += __shfl_xor_sync(0xffffffffu, c, 1);
-    return c;
-}
-__device__ __forceinline__ uint32_t reduced_value_index(uint32_t lane)
-{
-    return ((lane >> 4) & 1u) * 4u + ((lane >> 3) & 1u) * 2u + ((lane >> 2) & 1u);
-}
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
 {
@@ -427,15 +385,13 @@ struct Follower {
 };
 __device__ __forceinline__ void ring_put(const Shared &sm, uint32_t pw, uint32_t index, const Item &it)
 {
-    uint4 *dst = reinterpret_cast<uint4 *>(sm.ptr + kSmItems) + (pw * 16u + (index & 15u)) * 2u;
-    dst[0] = make_uint4(it.token, it.batch, (uint32_t)it.position, it.tile_begin);
-    dst[1] = make_uint4(it.tile_end, it.part, it.nparts, it.first_cta);
+    reinterpret_cast<uint4 *>(sm.ptr + kSmItems)[pw * 16u + (index & 15u)] =
+        make_uint4(it.batch, (uint32_t)it.position, it.tile_begin, it.tile_end);
 }
 __device__ __forceinline__ void follower_load(Follower &f, const Shared &sm, uint32_t pw)
 {
-    const uint4 *src = reinterpret_cast<const uint4 *>(sm.ptr + kSmItems) + (pw * 16u + (f.item & 15u)) * 2u;
-    const uint4 a = src[0], b = src[1];
-    f.batch = a.y; f.position = (int32_t)a.z; f.j = a.w; f.tile_end = b.x;
+    const uint4 a = reinterpret_cast<const uint4 *>(sm.ptr + kSmItems)[pw * 16u + (f.item & 15u)];
+    f.batch = a.x; f.position = (int32_t)a.y; f.j = a.z; f.tile_end = a.w;
 }
 __device__ __forceinline__ void follower_init(Follower &f, const Shared &sm, uint32_t pw, uint32_t first, uint32_t end)
 {
@@ -464,7 +420,7 @@ struct Compaction {
     uint32_t mask, inclusive, total;
     bool active;
 };
-__device__ __forceinline__ void compaction_build(Compaction &k, const SharedKVArgs &p, const Item &it, uint32_t lane)
+__device__ __noinline__ void compaction_build(Compaction &k, const SharedKVArgs &p, const Item &it, uint32_t lane)
 {
     const uint32_t count = it.position < 0 ? 0u : (uint32_t)(it.position + 1) / 4u;
     k.active = count < p.topk && p.topk <= 1024u;
@@ -485,7 +441,7 @@ __device__ __forceinline__ void compaction_build(Compaction &k, const SharedKVAr
     k.total = __shfl_sync(0xffffffffu, k.inclusive, 31);
 }
 // Slot (0..topk) holding the s-th valid selection; s < total.
-__device__ __forceinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s, bool in_range)
+__device__ __noinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s, bool in_range)
 {
     uint32_t chunk = 0;
 #pragma unroll 8
@@ -526,17 +482,19 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 
 // Producer warps (four, one per SM sub-partition: the rate at which a warp can hand row fetches to
 // the TMA unit is limited per warp).  Warp w owns key slots 32 w .. 32 w + 31 of every tile, lane =
-// slot.  Three stages, each `kLookahead` tiles behind the previous one, so that the two dependent
-// global reads in front of a row fetch (top-k entry -> page-table entry -> row) are issued several
-// tiles before their results are needed:
-//   A  candidate logical row of this lane's slot          (tile n)
-//   B  range check + page-table lookup                    (tile n - kLookahead)
-//   C  row fetch into the ring stage                      (tile n - 2 kLookahead)
-// The loop is unrolled by the lookahead so that every value keeps its register from the load that
-// produces it to its use (a shifting queue would read, and so wait for, every value each iteration).
+// slot.  The two dependent global reads in front of a row fetch (top-k entry -> page-table entry ->
+// row) are issued several tiles before their results are needed:
+//   A  candidate logical row of this lane's slot                    (tile n)
+//   B  range check + page-table lookup                              (tile n - kLookahead)
+//   S  row id = page * rows-per-page + row in page, to a small ring (tile n - 2 kLookahead)
+//   C  row fetch into the KV ring stage                             (same tiles as S)
+// A, B and S are tiny and unrolled by the lookahead, so that every loaded value keeps its register
+// from the load that produces it to its use (a shifting queue would read, and so wait for, every
+// value each iteration); C is larger and exists once: it reads the row ids back from the ring.
 // Row fetch: one TMA gather of four consecutive slots x one 128-channel segment per lane
-// (lane = 4 * group + segment), or 16-byte cp.async copies when the page strides rule TMA out.
-constexpr int kLookahead = 4;
+// (lane = 4 * group + segment); for the compressed rows of a C128 layer, which fill whole pages,
+// four 4 KB page-segment boxes per warp; 16-byte cp.async copies when the page strides rule TMA out.
+constexpr int kLookahead = 2;          // two tiles (several microseconds) cover the latency of either read
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
 template <int RATIO, bool TMA>
@@ -556,61 +514,79 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
 
     const int32_t *ori_table = reinterpret_cast<const int32_t *>(p.oriTable);
     const int32_t *cmp_table = reinterpret_cast<const int32_t *>(p.cmpTable);
+    const uint32_t ori_rows_per_page = (uint32_t)(p.oriStride >> 9), cmp_rows_per_page = (uint32_t)(p.cmpStride >> 9);
+    volatile int32_t *row_ring = reinterpret_cast<volatile int32_t *>(sm.ptr + kSmRowIds) + pw * (kLookahead * 32) + lane;
     const uint32_t slot = pw * 32u + lane;
     int32_t cand[kLookahead];             // stage A -> B, index = tile % kLookahead
-    int32_t page[kLookahead];             // stage B -> C: page id ...
-    int32_t offs[kLookahead];             // ... and row within the page, or -1 when the slot holds no key
+    int32_t page[kLookahead];             // stage B -> S: page id ...
+    int32_t offs[kLookahead];             // ... and row within the page (bit 8: original cache), or -1 without a key
 #pragma unroll
     for (int u = 0; u < kLookahead; ++u) { cand[u] = -1; page[u] = 0; offs[u] = -1; }
     uint32_t issued = 0;                  // tiles whose fetches have been issued
     uint32_t signalled = 0;               // cp.async path: tiles whose "full" barrier this thread has arrived on
 
-    bool finished = false;
-    for (uint32_t base = 0; !finished; base += (uint32_t)kLookahead) {
+    for (uint32_t base = 0;; base += (uint32_t)kLookahead) {
 #pragma unroll
-      for (int u = 0; u < kLookahead; ++u) {
-        const uint32_t n = base + (uint32_t)u;
-        const int32_t page_c = page[u], off_c = offs[u];
-        // ---- stage B: range check and page-table lookup for tile n - kLookahead
-        int32_t off_b = -1, page_b = 0;
-        if (n >= (uint32_t)kLookahead && !cb.done) {
-            const bool ori = cb.j == 0;
-            const uint32_t limit = ori ? 0x7fffffffu
-                                       : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
-            const int32_t c = cand[u];
-            if (c >= 0 && (uint32_t)c < limit) {
-                off_b = c & 31;
-                page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
-                             : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
+        for (int u = 0; u < kLookahead; ++u) {
+            const uint32_t n = base + (uint32_t)u;
+            // ---- stage S: row id of tile n - 2 kLookahead
+            {
+                const int32_t o = offs[u], pg = page[u];
+                int32_t id = kRowsInMap;
+                if (o >= 0) {
+                    const bool ori = (o >> 8) & 1;
+                    if (!(ori && (uint32_t)pg >= p.oriPages))         // never read outside the original cache
+                        id = !TMA ? (int32_t)(((uint32_t)pg << 5) + ((uint32_t)o & 31u))       // page, row in page
+                             : (RATIO == 128 && !ori)
+                                 ? pg                                                          // whole-page fetch
+                                 : (int32_t)((uint32_t)pg * (ori ? ori_rows_per_page : cmp_rows_per_page) + ((uint32_t)o & 31u));
+                }
+                row_ring[u * 32] = id;
             }
-            follower_advance(cb, sm, pw);
-        }
-        page[u] = page_b;
-        offs[u] = off_b;
-        // ---- stage A: candidate row for tile n
-        int32_t cand_a = -1;
-        if (!ca.done) {
-            cand_a = candidate_row<RATIO>(p, ca, comp, slot);
-            if (cursor_advance(ca, items)) {
-                ring_put(sm, pw, ca.item, ca.it);
-                if (RATIO == 4) compaction_build(comp, p, ca.it, lane);
+            // ---- stage B: range check and page-table lookup for tile n - kLookahead
+            int32_t off_b = -1, page_b = 0;
+            if (n >= (uint32_t)kLookahead && !cb.done) {
+                const bool ori = cb.j == 0;
+                const uint32_t limit = ori ? 0x7fffffffu
+                                           : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
+                const int32_t c = cand[u];
+                if (c >= 0 && (uint32_t)c < limit) {
+                    off_b = (c & 31) | (ori ? 256 : 0);
+                    page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
+                                 : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
+                }
+                follower_advance(cb, sm, pw);
             }
+            page[u] = page_b;
+            offs[u] = off_b;
+            // ---- stage A: candidate row for tile n
+            int32_t cand_a = -1;
+            if (!ca.done) {
+                cand_a = candidate_row<RATIO>(p, ca, comp, slot);
+                if (cursor_advance(ca, items)) {
+                    ring_put(sm, pw, ca.item, ca.it);
+                    if (RATIO == 4) compaction_build(comp, p, ca.it, lane);
+                }
+            }
+            cand[u] = cand_a;
         }
-        cand[u] = cand_a;
-        // ---- stage C: fetch the rows of tile n - 2 kLookahead
-        if (n >= 2u * kLookahead) {
-            if (cc.done) { finished = true; break; }
+        if (base < 2u * kLookahead) continue;
+        // ---- stage C: fetch the rows of tiles base - 2 kLookahead .. + kLookahead - 1
+#pragma unroll 1
+        for (uint32_t u = 0; u < (uint32_t)kLookahead; ++u) {
+            if (cc.done) goto drain;
             const uint32_t stage = issued % kStages, pass = issued / kStages;
             if (!wait_phase(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
             const bool ori = cc.j == 0;
-            const bool valid = off_c >= 0 && !(ori && (uint32_t)page_c >= p.oriPages);   // never read outside the original cache
+            const int32_t id = row_ring[u * 32];
+            const bool valid = id != kRowsInMap;
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
             if (lane == 0) reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + pw] = mask;
             const uint32_t tile = sm.base + kSmKv + stage * kTileBytes;
             if (TMA && RATIO == 128 && !ori) {
                 // the 32 slots of this warp are one page of the compressed cache: four 4 KB boxes
                 const bool any = mask != 0;
-                const int32_t page_id = __shfl_sync(0xffffffffu, page_c, 0);      // slot 32 w is the first to be valid
+                const int32_t page_id = __shfl_sync(0xffffffffu, id, 0);      // slot 32 w is the first to be valid
                 if (lane == 0) mbar_arrive_expect_tx(sm.bar(kBarFull + stage), any ? 16384u : 0u);
                 __syncwarp();
                 if (any && lane < 4)
@@ -618,11 +594,9 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                                      sm.bar(kBarFull + stage));
                 ++issued;
             } else if (TMA) {
-                const uint32_t rows_per_page = (uint32_t)((ori ? p.oriStride : p.cmpStride) >> 9);
-                const int32_t gid = valid ? (int32_t)((uint32_t)page_c * rows_per_page + (uint32_t)off_c) : kRowsInMap;
                 const uint32_t g = lane >> 2, seg = lane & 3u;
-                const int32_t r0 = __shfl_sync(0xffffffffu, gid, 4 * g), r1 = __shfl_sync(0xffffffffu, gid, 4 * g + 1);
-                const int32_t r2 = __shfl_sync(0xffffffffu, gid, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, gid, 4 * g + 3);
+                const int32_t r0 = __shfl_sync(0xffffffffu, id, 4 * g), r1 = __shfl_sync(0xffffffffu, id, 4 * g + 1);
+                const int32_t r2 = __shfl_sync(0xffffffffu, id, 4 * g + 2), r3 = __shfl_sync(0xffffffffu, id, 4 * g + 3);
                 const bool issue = ((mask >> (4u * g)) & 15u) != 0;
                 const uint32_t bytes = 512u * __popc(__ballot_sync(0xffffffffu, issue));
                 if (lane == 0) mbar_arrive_expect_tx(sm.bar(kBarFull + stage), bytes);
@@ -635,10 +609,10 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 ++issued;
             } else {
                 const uint64_t src = !valid ? 0ull
-                    : (ori ? p.ori + (uint64_t)(uint32_t)page_c * p.oriStride : p.cmp + (uint64_t)(uint32_t)page_c * p.cmpStride)
-                      + (uint64_t)(uint32_t)off_c * kDim;
+                    : (ori ? p.ori + (uint64_t)((uint32_t)id >> 5) * p.oriStride : p.cmp + (uint64_t)((uint32_t)id >> 5) * p.cmpStride)
+                      + (uint64_t)((uint32_t)id & 31u) * kDim;
                 const uint32_t lo = (uint32_t)src, hi = (uint32_t)(src >> 32);
-#pragma unroll 4
+#pragma unroll 1
                 for (uint32_t r = 0; r < 32u; ++r) {
                     if (!((mask >> r) & 1u)) continue;
                     const uint64_t rsrc = ((uint64_t)__shfl_sync(0xffffffffu, hi, r) << 32) | __shfl_sync(0xffffffffu, lo, r);
@@ -655,8 +629,8 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             }
             follower_advance(cc, sm, pw);
         }
-      }
     }
+drain:
     if (TMA) return;
     cp_async_wait<0>();
     fence_proxy_async_smem();
@@ -678,29 +652,45 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
     cursor_init(cq, items, first, end);
     uint32_t t = 0;                        // tiles issued so far
     for (uint32_t k = 0; !cq.done; ++k) {
-        if (!wait_phase(sm, kBarQReady, k & 1u)) return;      // this item's query codes are in shared memory
+        // Query codes: one buffer for the original kind (read by an item's first tile only) and two
+        // alternating buffers for the compressed kind, so that the next item is encoded while this
+        // one is processed.  Per item and kind this thread waits once for "encoded" and signals once
+        // "no longer read" (a commit behind the last MMA that reads the buffer, or a plain arrival
+        // when the item has no tile of that kind).
+        const bool uses_ori = cq.it.tile_begin == 0, uses_cmp = cq.it.tile_end > max(cq.it.tile_begin, 1u);
+        const uint32_t last = cq.it.tile_end - 1u;
+        const uint32_t cbuf = 1u + (k & 1u), cphase = (k >> 1) & 1u;     // compressed-kind buffer of this item
+        bool cmp_ready = false;
+        if (!wait_phase(sm, kBarQReady + 0, k & 1u)) return;
+        if (!uses_ori) mbar_arrive(sm.bar(kBarQFree + 0));
+        if (!uses_cmp) {
+            if (!wait_phase(sm, kBarQReady + cbuf, cphase)) return;
+            mbar_arrive(sm.bar(kBarQFree + cbuf));
+        }
         for (;;) {
             const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
+            const uint32_t j = cq.j;
+            if (j != 0 && !cmp_ready) {
+                if (!wait_phase(sm, kBarQReady + cbuf, cphase)) return;
+                cmp_ready = true;
+            }
             if (!wait_phase(sm, kBarFull + stage, (t / kStages) & 1u)) return;
             if (!wait_phase(sm, kBarSFree + buf, ph ^ 1u)) return;
             tc_fence_after();
             const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-            const uint32_t qb = sm.base + kSmQ + (cq.j == 0 ? 0u : 8192u);
+            const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : cbuf * 8192u);
             const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
-#ifdef SHAREDKV_TIMING
-            const long long t_issue = clock64();
-#endif
+            // the address field counts 16-byte units; offsets stay inside the 14-bit field
+#pragma unroll 1
+            for (uint32_t seg = 0; seg < 4; ++seg) {
 #pragma unroll
-            for (uint32_t ks = 0; ks < 16; ++ks) {
-                const uint32_t seg = ks >> 2, part = ks & 3u;
-                // the address field counts 16-byte units; offsets stay inside the 14-bit field
-                mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
-                       kIdescQK, ks);
+                for (uint32_t part = 0; part < 4; ++part)
+                    mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
+                           kIdescQK, seg | part);
             }
             mma_commit(sm.bar(kBarSFull + buf));
-#ifdef SHAREDKV_TIMING
-            timing_add(35, clock64() - t_issue);
-#endif
+            if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
+            else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
             ++t;
             if (cursor_advance(cq, items) || cq.done) break;
         }
@@ -724,7 +714,7 @@ __device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *item
         const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
         const uint32_t pb = sm.base + kSmP + buf * 2048u;
         const uint64_t a0 = smem_desc(kv, kSegBytes, 1024u, kSwizzle128), b0 = smem_desc(pb, 128u, 2048u, kSwizzleNone);
-#pragma unroll
+#pragma unroll 1
         for (uint32_t mb = 0; mb < 4; ++mb) {
 #pragma unroll
             for (uint32_t kk = 0; kk < 4; ++kk)
@@ -780,67 +770,97 @@ __device__ __forceinline__ float warp_reduce4(const float (&v)[4], uint32_t lane
     return c;   // value index = 2 * bit4 + bit3 of the lane
 }
 
-__device__ __forceinline__ void load_query_slice(const SharedKVArgs &p, uint32_t token, uint32_t t, uint4 (&raw)[4])
-{
-    const uint32_t h = t >> 4, d0 = (t & 15u) * 32u;
-    const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((uint64_t)token * 8u + h) * 1024u + d0 * 2u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) raw[i] = __ldg(src + i);
-}
-
-// Fold the cache scale of `kind` into this thread's 32 query channels (head t / 16, channels
-// 32 (t % 16) ..) and write the two INT8 code planes of that head (rows h and 8 + h of the
-// 16-row B operand) into swizzled shared memory.
+// ------------------------------------------------------------------ query warps (18, 19)
+// One warp per cache kind.  Lane l owns channels 16 l .. 16 l + 15 (one 16-byte chunk of a code
+// row).  Per item: fold the kind's cache scale into the eight query rows, split each into two INT8
+// code planes (rows h and 8 + h of the 16-row B operand, swizzled) and publish alpha * softmax_scale
+// per head.  Runs one item ahead of the S = K.Q^T issuer.
 template <bool DEBUG>
-__device__ __forceinline__ void encode_query(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm,
-                                             const uint4 (&raw)[4], uint32_t kind, uint32_t token, uint32_t t)
+__device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
+                           uint32_t first, uint32_t end, uint32_t kind, uint32_t lane)
 {
-    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale) + kind * 512u;
-    const uint32_t h = t >> 4, slice = t & 15u, d0 = slice * 32u;
-    const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw);
-    float amax = 0.f;
+    float sc[16];
+    {
+        const float4 *src = reinterpret_cast<const float4 *>(kind ? p.cmpScale : p.oriScale) + lane * 4u;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float f0 = __fmul_rn(__uint_as_float(rw[i] << 16), scales[d0 + 2 * i]);
-        const float f1 = __fmul_rn(__uint_as_float(rw[i] & 0xffff0000u), scales[d0 + 2 * i + 1]);
-        amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+        for (int i = 0; i < 4; ++i) {
+            const float4 v = __ldg(src + i);
+            sc[4 * i] = v.x; sc[4 * i + 1] = v.y; sc[4 * i + 2] = v.z; sc[4 * i + 3] = v.w;
+        }
     }
+    Cursor cur;
+    cursor_init(cur, items, first, end);
+    for (uint32_t k = 0; !cur.done; ++k) {
+        const Item it = cur.it;
+        const bool used = kind == 0 ? it.tile_begin == 0 : it.tile_end > max(it.tile_begin, 1u);
+        // buffer, and the use of it that must be over before it is rewritten
+        const uint32_t qbuf = kind == 0 ? 0u : 1u + (k & 1u);
+        const uint32_t uses_before = kind == 0 ? k : k >> 1;
+        char *qdst = sm.ptr + kSmQ + qbuf * 8192u;
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.q + (uint64_t)it.token * 8192u) + lane * 2u;
+        uint4 raw[4][2];                           // four heads at a time keeps the warp inside its register budget
+        if (used) {
 #pragma unroll
-    for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-    const float alpha = fmaxf(__fmul_rn(amax, kInv127), 1e-12f);
-    const float rcp = __frcp_rn(alpha);
-    char *qdst = sm.ptr + kSmQ + kind * 8192u;
+            for (int h = 0; h < 4; ++h) { raw[h][0] = __ldg(src + h * 64); raw[h][1] = __ldg(src + h * 64 + 1); }
+        }
+        if (uses_before > 0 && !wait_phase(sm, kBarQFree + qbuf, (uses_before - 1u) & 1u)) return;     // earlier codes are no longer read
+        if (used) {
+            float *alphas = reinterpret_cast<float *>(sm.ptr + kSmAlpha) + (k & 7u) * 16u + kind * 8u;
+#pragma unroll 1
+            for (uint32_t batch = 0; batch < 2; ++batch) {
+                if (batch == 1) {
 #pragma unroll
-    for (uint32_t c = 0; c < 2; ++c) {
-        uint32_t hi[4], lo[4];
+                    for (int h = 0; h < 4; ++h) { raw[h][0] = __ldg(src + (4 + h) * 64); raw[h][1] = __ldg(src + (4 + h) * 64 + 1); }
+                }
+#pragma unroll 1
+                for (uint32_t hh = 0; hh < 4; ++hh) {
+                    const uint32_t h = batch * 4u + hh;
+                    // rotate the four prefetched heads through slot 0 so that the loop body exists once
+                    const uint32_t *rw = reinterpret_cast<const uint32_t *>(raw[0]);
+                    float f[16];
+                    float amax = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            int ch[4], cl[4];
+                    for (int i = 0; i < 8; ++i) {
+                        f[2 * i] = __fmul_rn(__uint_as_float(rw[i] << 16), sc[2 * i]);
+                        f[2 * i + 1] = __fmul_rn(__uint_as_float(rw[i] & 0xffff0000u), sc[2 * i + 1]);
+                        amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+                    }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = 16 * c + 4 * w + e;                    // channel within the slice
-                const uint32_t word = rw[i >> 1];
-                const float x = (i & 1) ? __uint_as_float(word & 0xffff0000u) : __uint_as_float(word << 16);
-                const float f = __fmul_rn(x, scales[d0 + i]);
-                const float nrm = fminf(fmaxf(__fmul_rn(f, rcp), -127.f), 127.f);
-                const float hf = rintf(nrm);
-                ch[e] = (int)hf;
-                cl[e] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
+                    for (int d = 16; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+                    const float alpha = fmaxf(__fmul_rn(amax, kInv127), 1e-12f);
+                    const float rcp = __frcp_rn(alpha);
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        int ch[4], cl[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float nrm = fminf(fmaxf(__fmul_rn(f[4 * w + e], rcp), -127.f), 127.f);
+                            const float hf = rintf(nrm);
+                            ch[e] = (int)hf;
+                            cl[e] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
+                        }
+                        hi[w] = pack4(ch[0], ch[1], ch[2], ch[3]);
+                        lo[w] = pack4(cl[0], cl[1], cl[2], cl[3]);
+                    }
+                    const uint4 vh = make_uint4(hi[0], hi[1], hi[2], hi[3]), vl = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4 *>(qdst + tile_offset(h, lane, 2048u)) = vh;
+                    *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, lane, 2048u)) = vl;
+                    if (DEBUG) {
+                        char *g = reinterpret_cast<char *>(dbg.qCodes) + ((uint64_t)it.token * 2u + kind) * 16u * 512u;
+                        *reinterpret_cast<uint4 *>(g + h * 512u + lane * 16u) = vh;
+                        *reinterpret_cast<uint4 *>(g + (8u + h) * 512u + lane * 16u) = vl;
+                    }
+                    if (lane == 0) alphas[h] = __fmul_rn(alpha, p.softmaxScale);
+                    raw[0][0] = raw[1][0]; raw[0][1] = raw[1][1]; raw[1][0] = raw[2][0]; raw[1][1] = raw[2][1];
+                    raw[2][0] = raw[3][0]; raw[2][1] = raw[3][1];
+                }
             }
-            hi[w] = pack4(ch[0], ch[1], ch[2], ch[3]);
-            lo[w] = pack4(cl[0], cl[1], cl[2], cl[3]);
+            fence_proxy_async_smem();
         }
-        const uint4 vh = make_uint4(hi[0], hi[1], hi[2], hi[3]), vl = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        const uint32_t chunk = slice * 2u + c;
-        *reinterpret_cast<uint4 *>(qdst + tile_offset(h, chunk, 2048u)) = vh;
-        *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, chunk, 2048u)) = vl;
-        if (DEBUG) {
-            char *g = reinterpret_cast<char *>(dbg.qCodes) + ((uint64_t)token * 2u + kind) * 16u * 512u;
-            *reinterpret_cast<uint4 *>(g + h * 512u + chunk * 16u) = vh;
-            *reinterpret_cast<uint4 *>(g + (8u + h) * 512u + chunk * 16u) = vl;
-        }
+        mbar_arrive(sm.bar(kBarQReady + qbuf));
+        cursor_next_item(cur, items);
     }
-    if (slice == 0) reinterpret_cast<float *>(sm.ptr + kSmAlpha)[kind * 8u + h] = __fmul_rn(alpha, p.softmaxScale);
 }
 
 template <int RATIO, bool DEBUG>
@@ -852,7 +872,6 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
     const uint32_t lane = key & 31u, warp = key >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
     float *red = reinterpret_cast<float *>(sm.ptr + kSmRed) + half * 32u;     // [2 parities][4 warps][4], per half
-    const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha);
     volatile uint32_t *misc = sm.misc();
     uint32_t group_phase = 0, all_phase = 0;
 
@@ -862,20 +881,13 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
 
     Cursor cur;
     cursor_init(cur, items, first, end);
-    uint4 raw[4];
-    if (!cur.done) load_query_slice(p, cur.it.token, key, raw);
 
     uint32_t gt = 0;                               // tiles consumed so far by this CTA
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
-        // each half encodes the query against one cache kind's scales
-        encode_query<DEBUG>(p, dbg, sm, raw, half, it.token, key);
-        fence_proxy_async_smem();
-        mbar_arrive(sm.bar(kBarQReady));
-        // next item's query rows travel while this item's tiles are processed
-        if (cur.item + 1 < cur.items_end) load_query_slice(p, cur.next_lo.x, key, raw);
-        if (!wait_phase(sm, kBarQReady, k & 1u)) return;     // both halves' alphas are written
-
+        // alpha * softmax_scale of this item's query rows; written by the query warps before the
+        // S product of the item's first tile of the kind was issued
+        const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha) + (k & 7u) * 16u;
         float m[4], l[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -1012,7 +1024,6 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
     char *ws = reinterpret_cast<char *>(p.workspace);
     uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
     float *partials = reinterpret_cast<float *>(ws + ws_partials(p.tokens));
-    const float *scales = reinterpret_cast<const float *>(sm.ptr + kSmScale);
     volatile uint32_t *misc = sm.misc();
     uint32_t group_phase = 0;
 
@@ -1022,7 +1033,8 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
     for (int kind = 0; kind < 2; ++kind)
 #pragma unroll
-        for (int mb = 0; mb < 4; ++mb) sc[kind][mb] = __fmul_rn(scales[kind * 512 + mb * 128 + ch], kInv127);
+        for (int mb = 0; mb < 4; ++mb)
+            sc[kind][mb] = __fmul_rn(__ldg(reinterpret_cast<const float *>(kind ? p.cmpScale : p.oriScale) + mb * 128 + ch), kInv127);
 
     // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
     {
@@ -1100,10 +1112,12 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         if (it.nparts == 1) {
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
-                const float l = fin[8 + h];
+                // one correctly rounded reciprocal per head instead of 32 divisions (differs from the
+                // quotient by at most one FP32 ulp before the BF16 rounding)
+                const float inv = __frcp_rn(fin[8 + h]);
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb)
-                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], l));
+                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fmul_rn(acc[mb][h], inv));
             }
             if (lse && ch < 8) lse[ch] = __fadd_rn(fin[ch], logf(fin[8 + ch]));
             cursor_next_item(cur, items);
@@ -1151,10 +1165,12 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
                 }
             }
 #pragma unroll
-            for (int h = 0; h < 8; ++h)
+            for (int h = 0; h < 8; ++h) {
+                const float inv = __frcp_rn(den[h]);
 #pragma unroll
                 for (int mb = 0; mb < 4; ++mb)
-                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fdiv_rn(acc[mb][h], den[h]));
+                    out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fmul_rn(acc[mb][h], inv));
+            }
             if (lse && ch < 8) {
                 float mm = top[0], ll = den[0];
 #pragma unroll
@@ -1192,7 +1208,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
             mbar_init(sm.bar(kBarGroup + b), 128);          // one per softmax half
             mbar_init(sm.bar(kBarGroup + 2 + b), b == 0 ? 256 : 128);      // all softmax threads; all accumulate threads
         }
-        mbar_init(sm.bar(kBarQReady), 256);
+        for (uint32_t b = 0; b < 3; ++b) { mbar_init(sm.bar(kBarQReady + b), 32); mbar_init(sm.bar(kBarQFree + b), 1); }
         for (uint32_t i = 0; i < 8; ++i) { mbar_init(sm.bar(kBarRescale + i), 2); mbar_init(sm.bar(kBarItemDone + i), 2); }
         misc[1] = 0; misc[2] = 0; misc[3] = 0;
         fence_mbar_init();
@@ -1200,11 +1216,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     if (warp == kWarpMma) {
         tmem_alloc(sm.base + kSmMisc, kTmemCols);
         tmem_relinquish();
-    }
-    {
-        float *scales = reinterpret_cast<float *>(sm.ptr + kSmScale);
-        const float *os = reinterpret_cast<const float *>(p.oriScale), *cs = reinterpret_cast<const float *>(p.cmpScale);
-        for (uint32_t i = tid; i < 512u; i += kThreads) { scales[i] = os[i]; scales[512 + i] = cs[i]; }
     }
     tc_fence_before();
     __syncthreads();
@@ -1231,12 +1242,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         }
         producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - kWarpProducer, lane, &ori_map, &cmp_map, &cmp_page_map);
         cp_async_wait<0>();
-    } else {
+    } else if (warp < kWarpQuery) {
         if (lane == 0) {
             if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
             else mma_pv_loop(sm, cta_first, items, first, end, tmem);
         }
         __syncwarp();
+    } else {
+        query_loop<DEBUG>(p, dbg, sm, items, first, end, warp - kWarpQuery, lane);
     }
 #ifdef SHAREDKV_TIMING
     timing_add(39, clock64() - kernel_start);

@@ -1,0 +1,130 @@
+"""The drop-in boundary without a GPU: the C-ABI library loads and exports every symbol the
+header declares, struct layouts match the reference's, and the Python mirror keeps the
+reference's policy and validation behaviour (reference tests/npu/test_policy.py:18-34)."""
+import ctypes
+import os
+from pathlib import Path
+import re
+from types import SimpleNamespace
+from unittest.mock import patch
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def library():
+    from npu_sparse_attn_sharedkv_int8 import runtime
+    return runtime._library()
+
+
+def test_every_declared_symbol_is_exported():
+    header = (ROOT / "include" / "sharedkv_c_abi.h").read_text()
+    names = re.findall(r"SHAREDKV_API\s+[\w\s\*]+?\b(\w+)\s*\(", header)
+    assert len(names) >= 12
+    lib = library()
+    for name in names:
+        assert hasattr(lib, name), name
+
+
+def test_struct_layouts_match_the_reference_abi():
+    from npu_sparse_attn_sharedkv_int8.attention import _Args as AttentionArgs
+    from npu_sparse_attn_sharedkv_int8.cache import _Args as CacheArgs
+    lib = library()
+    assert ctypes.sizeof(AttentionArgs) == 200 == lib.sharedkv_attention_args_size()
+    assert ctypes.sizeof(CacheArgs) == 88 == lib.sharedkv_cache_args_size()
+    assert AttentionArgs.tokens.offset == 144 and AttentionArgs.softmaxScale.offset == 196
+    assert AttentionArgs.oriStride.offset == 112 and AttentionArgs.oriIndices.offset == 136
+    assert CacheArgs.tokens.offset == 64 and CacheArgs.pairedSlots.offset == 80
+    assert lib.sharedkv_attention_variant_count() == 23
+
+
+def test_workspace_formula_matches_library():
+    from npu_sparse_attn_sharedkv_int8 import c8_attention
+    lib = library()
+    for tokens in (1, 7, 64, 2048, 8192, 100000):
+        assert lib.sharedkv_workspace_bytes(tokens) == c8_attention.workspace_bytes(tokens)
+    assert c8_attention.WORKSPACE_BYTES == c8_attention.workspace_bytes(8192)
+
+
+def test_host_side_rejections_need_no_gpu():
+    lib = library()
+    null = ctypes.c_void_p(0)
+    assert lib.launch_cache_write(0, null, null) == -22
+    assert lib.launch_sharedkv_c8_sparse(0, null, null) == -22
+    assert lib.launch_sharedkv_c8_dense(0, null, null) == -22
+    assert lib.sharedkv_attention(0, 0, 20, -1, null) == -22
+    from npu_sparse_attn_sharedkv_int8.attention import _Args
+    args = _Args(tokens=4, batch=1, heads=8, ratio=4, window=128, oriBlock=32, cmpBlock=32, topk=1024)
+    assert lib.sharedkv_attention(ctypes.addressof(args), 0, 99, -1, null) == -2          # unknown variant
+    assert lib.sharedkv_attention(ctypes.addressof(args), 0, 20, -1, null) == -22         # null pointers
+    assert b"variant" in lib.sharedkv_status_string(-2)
+    assert b"invalid" in lib.sharedkv_status_string(-22)
+    empty = _Args()
+    assert lib.launch_sharedkv_c8_sparse(0, null, ctypes.byref(empty)) == 0               # zero tokens: nothing to do
+
+
+def test_route_selector_and_abi_guard():
+    from npu_sparse_attn_sharedkv_int8 import c8_attention
+    from npu_sparse_attn_sharedkv_int8.attention import _Args
+    with patch.dict(os.environ, {}, clear=True):
+        assert c8_attention.enabled()
+    for flag, expected in (("0", False), ("1", True)):
+        with patch.dict(os.environ, SHAREDKV_C8_DECODE=flag):
+            assert c8_attention.enabled() is expected
+    with patch.dict(os.environ, SHAREDKV_C8_DECODE="typo"), pytest.raises(ValueError):
+        c8_attention.enabled()
+    valid = dict(heads=8, tokens=48, batch=8, ratio=4, window=128, oriBlock=32, cmpBlock=32, oriIndices=0, topk=1024)
+    assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**valid)))
+    for key, value in (("tokens", 0), ("batch", 0), ("heads", 16), ("ratio", 1), ("window", 129), ("oriBlock", 64),
+                       ("cmpBlock", 64), ("oriIndices", 1), ("topk", 2048)):
+        assert not c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | {key: value}))))
+    for batch, tokens in ((9, 49), (23, 138), (128, 768), (1024, 8192)):
+        assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(batch=batch, tokens=tokens)))))
+    assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(ratio=128, topk=0)))))
+
+
+def test_cpu_tensors_are_rejected_not_emulated():
+    from npu_sparse_attn_sharedkv_int8 import PreparedAttention, PreparedCacheWrite
+    from tests.support import load_case
+    case, ori_scale, cmp_scale, _ = load_case("unit_c4")
+    with pytest.raises(ValueError, match="CUDA"):
+        PreparedAttention(case, ori_scale, cmp_scale)
+    cache = torch.zeros(2, 32, 1, 512, dtype=torch.int8)
+    with pytest.raises(ValueError, match="CUDA"):
+        PreparedCacheWrite(cache, torch.zeros(4, 512, dtype=torch.bfloat16), torch.zeros(4, dtype=torch.int32), torch.ones(512))
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from npu_sparse_attn_sharedkv_int8 import _paths
+    with patch.object(_paths, "NATIVE_DIR", tmp_path), pytest.raises(RuntimeError, match="Missing native library"):
+        _paths.native_path()
+
+
+def test_frozen_scale_contract():
+    from npu_sparse_attn_sharedkv_int8 import CacheQuantization
+    for bad in (0.0, -1.0, float("nan"), float("inf")):
+        scale = torch.ones(512)
+        scale[17] = bad
+        with pytest.raises(ValueError):
+            CacheQuantization(scale)
+    quant = CacheQuantization.calibrate([torch.ones(3, 512)])
+    before = quant.quantize(torch.linspace(-1, 1, 512).reshape(1, 512))
+    quant.quantize(torch.full((2, 512), 1000.0))
+    assert torch.equal(quant.quantize(torch.linspace(-1, 1, 512).reshape(1, 512)), before)
+    tensors = {"layer.kv_cache_scale": torch.ones(512), "layer.kv_cache_offset": torch.zeros(512)}
+    assert torch.equal(CacheQuantization.from_msmodelslim(tensors, "layer").scale, torch.ones(512))
+    tensors["layer.kv_cache_offset"][0] = 1
+    with pytest.raises(ValueError, match="nonzero offsets"):
+        CacheQuantization.from_msmodelslim(tensors, "layer")
+
+
+def test_request_sharding_is_balanced_and_complete():
+    import bench
+    lengths = bench.box_lengths(2048)
+    for ranks in (1, 2, 4, 8):
+        shards = bench.shard(lengths, ranks)
+        assert sorted(i for s in shards for i in s) == list(range(2048))
+        loads = [int((lengths[torch.tensor(s)] // 4 + lengths[torch.tensor(s)] // 128 + 256).sum()) for s in shards]
+        assert max(loads) <= 1.02 * (sum(loads) / ranks)
