@@ -273,12 +273,12 @@ struct Shared {
 
 #ifdef SHAREDKV_TIMING
 // Development aid (not built by default): cycles spent waiting, per CTA, per role and barrier.
-__device__ unsigned long long g_wait_cycles[kMaxCtas][240];
+__device__ unsigned long long g_wait_cycles[kMaxCtas][400];
 __device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
 {
     const uint32_t warp = threadIdx.x >> 5;
-    if ((threadIdx.x & 31u) == 0 && (warp & 3u) == 0)
-        atomicAdd(&g_wait_cycles[blockIdx.x][(warp >> 2) * 40u + slot], (unsigned long long)cycles);
+    if ((threadIdx.x & 31u) == 0 && ((warp & 3u) == 0 || warp >= 16))
+        atomicAdd(&g_wait_cycles[blockIdx.x][(warp < 16 ? (warp >> 2) : warp - 12u) * 50u + slot], (unsigned long long)cycles);
 }
 #endif
 
@@ -680,6 +680,9 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
             const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
             const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : cbuf * 8192u);
             const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
+#ifdef SHAREDKV_TIMING
+            const long long t_issue = clock64();
+#endif
             // the address field counts 16-byte units; offsets stay inside the 14-bit field
 #pragma unroll 1
             for (uint32_t seg = 0; seg < 4; ++seg) {
@@ -688,7 +691,14 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
                     mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
                            kIdescQK, seg | part);
             }
+#ifdef SHAREDKV_TIMING
+            const long long t_commit = clock64();
+            timing_add(44, t_commit - t_issue);
+#endif
             mma_commit(sm.bar(kBarSFull + buf));
+#ifdef SHAREDKV_TIMING
+            timing_add(45, clock64() - t_commit);
+#endif
             if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
             else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
             ++t;
@@ -968,6 +978,8 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 if (half == 0) reinterpret_cast<uint32_t *>(ring)[8] = rec;
                 mbar_arrive(sm.bar(kBarRescale + (gt & 7u)));
             }
+            // the O product that read this P buffer two tiles ago must be complete before it is rewritten
+            if (gt >= 2u && !wait_phase(sm, kBarOFull + buf, ph ^ 1u)) return;
             uint32_t *pdst = reinterpret_cast<uint32_t *>(sm.ptr + kSmP + buf * 2048u + key * 16u);
             const uint32_t c_hi = pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), c_lo = pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]);
             pdst[half] = c_hi;
@@ -1252,7 +1264,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         query_loop<DEBUG>(p, dbg, sm, items, first, end, warp - kWarpQuery, lane);
     }
 #ifdef SHAREDKV_TIMING
-    timing_add(39, clock64() - kernel_start);
+    timing_add(49, clock64() - kernel_start);
 #endif
     tc_fence_before();
     __syncthreads();
@@ -1370,7 +1382,7 @@ extern "C" __attribute__((visibility("default"))) int sharedkv_timing_read(unsig
 {
     cudaError_t e = cudaMemcpyFromSymbol(host, g_wait_cycles, sizeof(g_wait_cycles));
     if (e == cudaSuccess && reset) {
-        static unsigned long long zeros[kMaxCtas][240];
+        static unsigned long long zeros[kMaxCtas][400];
         e = cudaMemcpyToSymbol(g_wait_cycles, zeros, sizeof(zeros));
     }
     return (int)e;
