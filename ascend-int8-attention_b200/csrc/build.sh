@@ -8,5 +8,6 @@ NVCC=${NVCC:-/usr/local/cuda/bin/nvcc}
 "$NVCC" -std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a \
     -Xcompiler -fPIC -Xcompiler -fvisibility=hidden ${SHAREDKV_NVCC_FLAGS:-} \
     -shared -o "$out/libsharedkv_cuda.so" \
-    "$here/c_abi.cu" "$here/cache_write.cu" "$here/decode_attention.cu"
+    "$here/c_abi.cu" "$here/cache_write.cu" "$here/decode_attention.cu" \
+    "$here/attention_static_scratch.cu"
 echo "built $out/libsharedkv_cuda.so"

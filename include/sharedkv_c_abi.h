@@ -153,6 +153,29 @@ SHAREDKV_API int sharedkv_attention_debug(uint32_t variant, void *stream, const 
 /* Human-readable text for a value returned by any entry above. */
 SHAREDKV_API const char *sharedkv_status_string(int status);
 
+/* Decode attention without a caller-provided workspace.  No counterpart in the reference, whose
+ * callers always pass a workspace tensor (attention.py:171-184).
+ *
+ * For callers that cannot allocate device memory: a plugin that is only handed tensor pointers,
+ * or a thread that must stay out of its framework's allocator.  `args->workspace` is ignored (it
+ * may be 0); the scratch is one fixed array per device that is part of the library image, so this
+ * entry allocates nothing, not even on its first call.  Everything else (arguments, variants,
+ * results, status codes) is as for the launch_sharedkv_c8_* entries, and the results are
+ * bit-identical to theirs.
+ *
+ *   - Limit: args->tokens <= SHAREDKV_STATIC_SCRATCH_MAX_TOKENS, else SHAREDKV_ERANGE is returned
+ *     and nothing is launched.
+ *   - The first call on each device looks the array's address up (with that device current, which
+ *     is the caller's job as for every launch_* entry).  Make that first call outside any stream
+ *     capture; later calls only launch kernels.
+ *   - The array needs no clearing, before the first call or between calls: each call rebuilds
+ *     what it reads.
+ *   - All calls on a device share the array.  Calls on one stream are ordered and safe; calls that
+ *     can overlap in time (different streams or threads) race on it and give wrong results.  Use
+ *     the workspace-taking entries with one workspace per stream for those. */
+#define SHAREDKV_STATIC_SCRATCH_MAX_TOKENS 4096u
+SHAREDKV_API int sharedkv_attention_static_scratch(uint32_t variant, void *stream, const SharedKVArgs *args);
+
 #ifdef __cplusplus
 }
 #endif
