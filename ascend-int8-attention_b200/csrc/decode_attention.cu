@@ -57,9 +57,27 @@ constexpr uint32_t kTileKeys = 128;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
-constexpr uint32_t kThreads = 640;                        // 8 softmax + 4 accumulate + 4 producer + 2 MMA + 2 query warps
+constexpr uint32_t kThreads = 768;                        // 8 softmax + 4 accumulate + 2 x 4 producer + 2 MMA + 2 query warps
 constexpr uint32_t kWarpProducer = 12, kWarpMma = 16;   // warp 16 issues S = K.Q^T, warp 17 issues O = K^T.P
 constexpr uint32_t kWarpQuery = 18;                      // warps 18 / 19 encode the query for the original / compressed scales
+constexpr uint32_t kWarpProducerB = 20;                  // warps 12-15 fetch the even tiles of the CTA, warps 20-23 the odd ones
+// Registers per thread by role (the kernel starts every warp at 80; see registers_release/acquire).
+// Per SM sub-partition: 2 softmax + 1 accumulate + 2 producer + 1 MMA-or-query warp share 6 x 80 x 32 registers.
+constexpr uint32_t kRegsLaunch = 80;     // what __launch_bounds__(768, 1) lets the compiler use
+#ifndef SHAREDKV_REGS_SOFTMAX
+#define SHAREDKV_REGS_SOFTMAX 80
+#define SHAREDKV_REGS_ACCUMULATE 128
+#define SHAREDKV_REGS_PRODUCER 56
+#define SHAREDKV_REGS_ISSUE 80
+#endif
+constexpr uint32_t kRegsSoftmax = SHAREDKV_REGS_SOFTMAX, kRegsAccumulate = SHAREDKV_REGS_ACCUMULATE,
+                   kRegsProducer = SHAREDKV_REGS_PRODUCER, kRegsIssue = SHAREDKV_REGS_ISSUE;
+// The registers a CTA may re-divide are those it was launched with.  Asking for more than that
+// would leave registers_acquire waiting for ever.
+static_assert(2 * kRegsSoftmax + kRegsAccumulate + 2 * kRegsProducer + kRegsIssue <= 6 * kRegsLaunch,
+              "register budgets of one sub-partition's six warps exceed the launch allocation");
+static_assert(kRegsSoftmax >= kRegsLaunch && kRegsAccumulate >= kRegsLaunch && kRegsProducer <= kRegsLaunch && kRegsIssue <= kRegsLaunch,
+              "acquire only grows, release only shrinks");
 constexpr uint32_t kMaxCtas = 160;
 constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
@@ -77,9 +95,9 @@ constexpr uint32_t kSmRed = kSmMask + 64;                    // FP32 [2 halves][
 constexpr uint32_t kSmAlpha = kSmRed + 256;                  // FP32 [8 items][2 kinds][8]: alpha * softmax_scale
 constexpr uint32_t kSmRescale = kSmAlpha + 8 * 64;              // [8 tiles][16]: r[8], debug record, pad
 constexpr uint32_t kSmFinal = kSmRescale + 8 * 64;           // [8 items][16]: m[8], l[8]
-constexpr uint32_t kSmItems = kSmFinal + 8 * 64;             // producers: per warp a ring of 16 work items (16 B each)
-constexpr uint32_t kSmRowIds = kSmItems + 4 * 16 * 16;       // producers: per warp [lookahead][32 lanes] row ids
-constexpr uint32_t kSmBar = kSmRowIds + 4 * 2 * 32 * 4;      // mbarriers
+constexpr uint32_t kSmItems = kSmFinal + 8 * 64;             // producers: per warp set a ring of 16 work items (16 B each)
+constexpr uint32_t kSmRowIds = kSmItems + 2 * 16 * 16;       // producers: per warp [lookahead][32 lanes] row ids
+constexpr uint32_t kSmBar = kSmRowIds + 8 * 2 * 32 * 4;      // mbarriers
 constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kBarPReady = 10, kBarOFull = 12,
                    kBarOFree = 14, kBarQReady = 16 /* x3 query buffers */, kBarQFree = 19 /* x3 */,
                    kBarGroup = 22 /* x4: softmax halves, all softmax, all accumulate */,
@@ -273,18 +291,21 @@ struct Shared {
 
 #ifdef SHAREDKV_TIMING
 // Development aid (not built by default): cycles spent waiting, per CTA, per role and barrier.
-__device__ unsigned long long g_wait_cycles[kMaxCtas][400];
+__device__ unsigned long long g_wait_cycles[kMaxCtas][450];
 __device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
 {
     const uint32_t warp = threadIdx.x >> 5;
-    if ((threadIdx.x & 31u) == 0 && ((warp & 3u) == 0 || warp >= 16))
-        atomicAdd(&g_wait_cycles[blockIdx.x][(warp < 16 ? (warp >> 2) : warp - 12u) * 50u + slot], (unsigned long long)cycles);
+    if ((threadIdx.x & 31u) == 0 && ((warp & 3u) == 0 || (warp >= 16 && warp < 20)))
+        atomicAdd(&g_wait_cycles[blockIdx.x][(warp < 16 ? (warp >> 2) : warp < 20 ? warp - 12u : 8u) * 50u + slot], (unsigned long long)cycles);
 }
 #endif
 
 // Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.  The common case, a
 // phase that is already complete, is one instruction inline; the polling loop lives out of line so
 // that the many call sites stay small (the kernel's hot loops have to share the instruction cache).
+// ROLE (0 softmax, 1 accumulate, 2 producer, 3 issue/query) only makes one copy per register budget:
+// a function called from warps with different register allocations cannot be compiled.
+template <int ROLE>
 __device__ __noinline__ bool wait_phase_slow(uint32_t bar, uint32_t parity, volatile uint32_t *misc)
 {
     const long long start = clock64();
@@ -297,6 +318,7 @@ __device__ __noinline__ bool wait_phase_slow(uint32_t bar, uint32_t parity, vola
         }
     }
 }
+template <int ROLE>
 __device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
 {
     const uint32_t bar = sm.bar(bar_index);
@@ -304,7 +326,7 @@ __device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index,
     struct Scope { uint32_t i; long long t0; __device__ ~Scope() { timing_add(i, clock64() - t0); } } scope{bar_index, clock64()};
 #endif
     if (mbar_try_wait(bar, parity)) return true;
-    return wait_phase_slow(bar, parity, sm.misc());
+    return wait_phase_slow<ROLE>(bar, parity, sm.misc());
 }
 
 __device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
@@ -376,34 +398,55 @@ __device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items)
     return true;
 }
 // Trailing cursor of a producer warp: walks the same tiles as a leading Cursor, a bounded
-// number of items behind it, and takes the descriptors from the warp's shared-memory ring the
-// leader fills (every lane writes and later reads its own copy, so no synchronisation is involved).
+// number of items behind it, and takes the descriptors from a shared-memory ring the leader fills.
+// The four warps of a producer set share one ring: all of them write the same values, and a warp
+// only reads entries it has itself written before (the set's warps are never more than the KV
+// ring's three tiles apart, the leader runs eight tiles ahead, the ring holds 16 items), so no
+// synchronisation is involved.
 struct Follower {
     uint32_t item, items_end, j, tile_end, batch;
     int32_t position;
     bool done;
 };
-__device__ __forceinline__ void ring_put(const Shared &sm, uint32_t pw, uint32_t index, const Item &it)
+__device__ __forceinline__ void ring_put(const Shared &sm, uint32_t ring, uint32_t index, const Item &it)
 {
-    reinterpret_cast<uint4 *>(sm.ptr + kSmItems)[pw * 16u + (index & 15u)] =
+    reinterpret_cast<uint4 *>(sm.ptr + kSmItems)[ring * 16u + (index & 15u)] =
         make_uint4(it.batch, (uint32_t)it.position, it.tile_begin, it.tile_end);
 }
-__device__ __forceinline__ void follower_load(Follower &f, const Shared &sm, uint32_t pw)
+__device__ __forceinline__ void follower_load(Follower &f, const Shared &sm, uint32_t ring)
 {
-    const uint4 a = reinterpret_cast<const uint4 *>(sm.ptr + kSmItems)[pw * 16u + (f.item & 15u)];
+    const uint4 a = reinterpret_cast<const uint4 *>(sm.ptr + kSmItems)[ring * 16u + (f.item & 15u)];
     f.batch = a.x; f.position = (int32_t)a.y; f.j = a.z; f.tile_end = a.w;
 }
-__device__ __forceinline__ void follower_init(Follower &f, const Shared &sm, uint32_t pw, uint32_t first, uint32_t end)
+__device__ __forceinline__ void follower_init(Follower &f, const Shared &sm, uint32_t ring, uint32_t first, uint32_t end)
 {
     f.item = first; f.items_end = end; f.done = first >= end;
     f.j = f.tile_end = f.batch = 0; f.position = 0;
-    if (!f.done) follower_load(f, sm, pw);
+    if (!f.done) follower_load(f, sm, ring);
 }
-__device__ __forceinline__ void follower_advance(Follower &f, const Shared &sm, uint32_t pw)
+__device__ __forceinline__ void follower_advance(Follower &f, const Shared &sm, uint32_t ring)
 {
     if (++f.j < f.tile_end) return;
     if (++f.item >= f.items_end) { f.done = true; return; }
-    follower_load(f, sm, pw);
+    follower_load(f, sm, ring);
+}
+// A producer set fetches every second tile of the CTA: its cursors move two tiles at a time.
+__device__ __forceinline__ void follower_advance2(Follower &f, const Shared &sm, uint32_t ring)
+{
+    follower_advance(f, sm, ring);
+    if (!f.done) follower_advance(f, sm, ring);
+}
+// Leading cursor: `steps` tiles on, publishing every item it enters; true when the item changed.
+__device__ __forceinline__ bool leader_advance(Cursor &c, const Item *items, const Shared &sm, uint32_t ring, uint32_t steps)
+{
+    bool moved = false;
+    for (uint32_t s = 0; s < steps && !c.done; ++s) {
+        if (cursor_advance(c, items)) {
+            ring_put(sm, ring, c.item, c.it);
+            moved = true;
+        }
+    }
+    return moved;
 }
 // Skip whatever is left of the current item.
 __device__ __forceinline__ void cursor_next_item(Cursor &c, const Item *items)
@@ -499,15 +542,21 @@ constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps s
 
 template <int RATIO, bool TMA>
 __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, uint32_t first, uint32_t end,
-                              uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
+                              uint32_t set, uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
                               const CUtensorMap *cmp_page_map)
 {
+    // set 0 fetches tiles 0, 2, 4 ... of the CTA, set 1 tiles 1, 3, 5 ...
     Cursor ca;
     cursor_init(ca, items, first, end);
-    if (!ca.done) ring_put(sm, pw, ca.item, ca.it);
+    if (!ca.done) ring_put(sm, set, ca.item, ca.it);
+    if (set) leader_advance(ca, items, sm, set, 1);
     Follower cb, cc;
-    follower_init(cb, sm, pw, first, end);
-    follower_init(cc, sm, pw, first, end);
+    follower_init(cb, sm, set, first, end);
+    follower_init(cc, sm, set, first, end);
+    if (set && !cb.done) {
+        follower_advance(cb, sm, set);
+        follower_advance(cc, sm, set);
+    }
     Compaction comp;
     comp.active = false; comp.mask = comp.inclusive = comp.total = 0;
     if (RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
@@ -515,7 +564,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
     const int32_t *ori_table = reinterpret_cast<const int32_t *>(p.oriTable);
     const int32_t *cmp_table = reinterpret_cast<const int32_t *>(p.cmpTable);
     const uint32_t ori_rows_per_page = (uint32_t)(p.oriStride >> 9), cmp_rows_per_page = (uint32_t)(p.cmpStride >> 9);
-    volatile int32_t *row_ring = reinterpret_cast<volatile int32_t *>(sm.ptr + kSmRowIds) + pw * (kLookahead * 32) + lane;
+    volatile int32_t *row_ring = reinterpret_cast<volatile int32_t *>(sm.ptr + kSmRowIds) + (set * 4u + pw) * (kLookahead * 32) + lane;
     const uint32_t slot = pw * 32u + lane;
     int32_t cand[kLookahead];             // stage A -> B, index = tile % kLookahead
     int32_t page[kLookahead];             // stage B -> S: page id ...
@@ -555,7 +604,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                     page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
                                  : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
                 }
-                follower_advance(cb, sm, pw);
+                follower_advance2(cb, sm, set);
             }
             page[u] = page_b;
             offs[u] = off_b;
@@ -563,10 +612,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             int32_t cand_a = -1;
             if (!ca.done) {
                 cand_a = candidate_row<RATIO>(p, ca, comp, slot);
-                if (cursor_advance(ca, items)) {
-                    ring_put(sm, pw, ca.item, ca.it);
-                    if (RATIO == 4) compaction_build(comp, p, ca.it, lane);
-                }
+                if (leader_advance(ca, items, sm, set, 2) && RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
             }
             cand[u] = cand_a;
         }
@@ -575,8 +621,9 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
 #pragma unroll 1
         for (uint32_t u = 0; u < (uint32_t)kLookahead; ++u) {
             if (cc.done) goto drain;
-            const uint32_t stage = issued % kStages, pass = issued / kStages;
-            if (!wait_phase(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
+            const uint32_t t = 2u * issued + set;          // position of the tile in the CTA's sequence
+            const uint32_t stage = t % kStages, pass = t / kStages;
+            if (!wait_phase<2>(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
             const bool ori = cc.j == 0;
             const int32_t id = row_ring[u * 32];
             const bool valid = id != kRowsInMap;
@@ -623,11 +670,11 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 if (issued - signalled == 2) {            // keep one tile in flight behind the newest
                     cp_async_wait<1>();
                     fence_proxy_async_smem();
-                    mbar_arrive(sm.bar(kBarFull + signalled % kStages));
+                    mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % kStages));
                     ++signalled;
                 }
             }
-            follower_advance(cc, sm, pw);
+            follower_advance2(cc, sm, set);
         }
     }
 drain:
@@ -635,7 +682,7 @@ drain:
     cp_async_wait<0>();
     fence_proxy_async_smem();
     while (signalled < issued) {
-        mbar_arrive(sm.bar(kBarFull + signalled % kStages));
+        mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % kStages));
         ++signalled;
     }
 }
@@ -648,34 +695,38 @@ drain:
 __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
+    const bool leader = elect_one();
+    first = __shfl_sync(0xffffffffu, first, 0);        // loop bounds the compiler can see are the same in all lanes
+    end = __shfl_sync(0xffffffffu, end, 0);
     Cursor cq;
     cursor_init(cq, items, first, end);
     uint32_t t = 0;                        // tiles issued so far
-    for (uint32_t k = 0; !cq.done; ++k) {
+    for (uint32_t k = 0; k < end - first; ++k) {
         // Query codes: one buffer for the original kind (read by an item's first tile only) and two
         // alternating buffers for the compressed kind, so that the next item is encoded while this
         // one is processed.  Per item and kind this thread waits once for "encoded" and signals once
         // "no longer read" (a commit behind the last MMA that reads the buffer, or a plain arrival
         // when the item has no tile of that kind).
-        const bool uses_ori = cq.it.tile_begin == 0, uses_cmp = cq.it.tile_end > max(cq.it.tile_begin, 1u);
-        const uint32_t last = cq.it.tile_end - 1u;
+        const uint32_t tile_begin = __shfl_sync(0xffffffffu, cq.it.tile_begin, 0), tile_end = __shfl_sync(0xffffffffu, cq.it.tile_end, 0);
+        const bool uses_ori = tile_begin == 0, uses_cmp = tile_end > max(tile_begin, 1u);
+        const uint32_t last = tile_end - 1u;
+        uint32_t j = tile_begin;
         const uint32_t cbuf = 1u + (k & 1u), cphase = (k >> 1) & 1u;     // compressed-kind buffer of this item
         bool cmp_ready = false;
-        if (!wait_phase(sm, kBarQReady + 0, k & 1u)) return;
-        if (!uses_ori) mbar_arrive(sm.bar(kBarQFree + 0));
+        if (!wait_phase<3>(sm, kBarQReady + 0, k & 1u)) return;
+        if (!uses_ori && leader) mbar_arrive(sm.bar(kBarQFree + 0));
         if (!uses_cmp) {
-            if (!wait_phase(sm, kBarQReady + cbuf, cphase)) return;
-            mbar_arrive(sm.bar(kBarQFree + cbuf));
+            if (!wait_phase<3>(sm, kBarQReady + cbuf, cphase)) return;
+            if (leader) mbar_arrive(sm.bar(kBarQFree + cbuf));
         }
-        for (;;) {
+        for (; j < tile_end; ++j) {
             const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-            const uint32_t j = cq.j;
             if (j != 0 && !cmp_ready) {
-                if (!wait_phase(sm, kBarQReady + cbuf, cphase)) return;
+                if (!wait_phase<3>(sm, kBarQReady + cbuf, cphase)) return;
                 cmp_ready = true;
             }
-            if (!wait_phase(sm, kBarFull + stage, (t / kStages) & 1u)) return;
-            if (!wait_phase(sm, kBarSFree + buf, ph ^ 1u)) return;
+            if (!wait_phase<3>(sm, kBarFull + stage, (t / kStages) & 1u)) return;
+            if (!wait_phase<3>(sm, kBarSFree + buf, ph ^ 1u)) return;
             tc_fence_after();
             const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
             const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : cbuf * 8192u);
@@ -688,22 +739,25 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
             for (uint32_t seg = 0; seg < 4; ++seg) {
 #pragma unroll
                 for (uint32_t part = 0; part < 4; ++part)
-                    mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
-                           kIdescQK, seg | part);
+                    if (leader)
+                        mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
+                               kIdescQK, seg | part);
             }
 #ifdef SHAREDKV_TIMING
             const long long t_commit = clock64();
             timing_add(44, t_commit - t_issue);
 #endif
-            mma_commit(sm.bar(kBarSFull + buf));
+            if (leader) mma_commit(sm.bar(kBarSFull + buf));
 #ifdef SHAREDKV_TIMING
             timing_add(45, clock64() - t_commit);
 #endif
-            if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
-            else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
+            if (leader) {
+                if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
+                else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
+            }
             ++t;
-            if (cursor_advance(cq, items) || cq.done) break;
         }
+        cursor_next_item(cq, items);
     }
 }
 
@@ -711,15 +765,17 @@ __device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *item
 {
     constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
     // only the number of tiles matters here
+    const bool leader = elect_one();
     uint32_t tiles = 0;
     for (uint32_t k = first; k < end; ++k) {
         const Item it = load_item(items, k);
         tiles += it.tile_end - it.tile_begin;
     }
+    tiles = __shfl_sync(0xffffffffu, tiles, 0);
     for (uint32_t t = 0; t < tiles; ++t) {
         const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-        if (!wait_phase(sm, kBarPReady + buf, ph)) return;
-        if (!wait_phase(sm, kBarOFree + buf, ph ^ 1u)) return;
+        if (!wait_phase<3>(sm, kBarPReady + buf, ph)) return;
+        if (!wait_phase<3>(sm, kBarOFree + buf, ph ^ 1u)) return;
         tc_fence_after();
         const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
         const uint32_t pb = sm.base + kSmP + buf * 2048u;
@@ -728,11 +784,14 @@ __device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *item
         for (uint32_t mb = 0; mb < 4; ++mb) {
 #pragma unroll
             for (uint32_t kk = 0; kk < 4; ++kk)
-                mma_i8(tmem + kColO + buf * 64u + mb * 16u, a0 + ((mb * kSegBytes + kk * 4096u) >> 4), b0 + ((kk * 512u) >> 4),
-                       kIdescPV, kk);
+                if (leader)
+                    mma_i8(tmem + kColO + buf * 64u + mb * 16u, a0 + ((mb * kSegBytes + kk * 4096u) >> 4), b0 + ((kk * 512u) >> 4),
+                           kIdescPV, kk);
         }
-        mma_commit(sm.bar(kBarOFull + buf));
-        mma_commit(sm.bar(kBarEmpty + stage));      // the stage's last reader (its S product finished before P existed)
+        if (leader) {
+            mma_commit(sm.bar(kBarOFull + buf));
+            mma_commit(sm.bar(kBarEmpty + stage));      // the stage's last reader (its S product finished before P existed)
+        }
     }
 }
 
@@ -741,10 +800,11 @@ __device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *item
 // every tile: columns 4 half + i (high plane) and 8 + 4 half + i (low plane) of S.
 
 // Wait-capable rendezvous of `which`'s threads (an mbarrier wait can time out, a bar.sync cannot).
+template <int ROLE>
 __device__ __forceinline__ bool group_sync(const Shared &sm, uint32_t which, uint32_t &phase)
 {
     mbar_arrive(sm.bar(kBarGroup + which));
-    const bool ok = wait_phase(sm, kBarGroup + which, phase);
+    const bool ok = wait_phase<ROLE>(sm, kBarGroup + which, phase);
     phase ^= 1u;
     return ok;
 }
@@ -813,7 +873,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
 #pragma unroll
             for (int h = 0; h < 4; ++h) { raw[h][0] = __ldg(src + h * 64); raw[h][1] = __ldg(src + h * 64 + 1); }
         }
-        if (uses_before > 0 && !wait_phase(sm, kBarQFree + qbuf, (uses_before - 1u) & 1u)) return;     // earlier codes are no longer read
+        if (uses_before > 0 && !wait_phase<3>(sm, kBarQFree + qbuf, (uses_before - 1u) & 1u)) return;     // earlier codes are no longer read
         if (used) {
             float *alphas = reinterpret_cast<float *>(sm.ptr + kSmAlpha) + (k & 7u) * 16u + kind * 8u;
 #pragma unroll 1
@@ -907,10 +967,10 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
             const uint32_t kind = j == 0 ? 0u : 1u;
             const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
-            if (!wait_phase(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
+            if (!wait_phase<0>(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
             const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
             const bool valid = (mask_word >> lane) & 1u;
-            if (!wait_phase(sm, kBarSFull + buf, ph)) return;
+            if (!wait_phase<0>(sm, kBarSFull + buf, ph)) return;
             tc_fence_after();
             uint32_t s_hi[4], s_lo[4];
             tmem_ld4(tmem_lane + kColS + buf * 16u + half * 4u, s_hi);
@@ -922,9 +982,9 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             uint32_t rec = 0;
             if (DEBUG) {
                 if (threadIdx.x == 0) misc[2] = atomicAdd(reinterpret_cast<uint32_t *>(dbg.counter), 1u);
-                if (!group_sync(sm, 2, all_phase)) return;
+                if (!group_sync<0>(sm, 2, all_phase)) return;
                 rec = misc[2];
-                if (!group_sync(sm, 2, all_phase)) return;      // everyone has read the record before the next is drawn
+                if (!group_sync<0>(sm, 2, all_phase)) return;      // everyone has read the record before the next is drawn
                 if (rec < dbg.maxTiles) {
                     if (threadIdx.x == 0) {
                         int32_t *info = reinterpret_cast<int32_t *>(dbg.tileInfo) + (uint64_t)rec * 4u;
@@ -946,7 +1006,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             const float wmax = warp_reduce4<true>(logit, lane);
             float *slot_red = red + (gt & 1u) * 16u;
             if ((lane & 7u) == 0) slot_red[warp * 4u + (lane >> 3)] = wmax;
-            if (!group_sync(sm, half, group_phase)) return;
+            if (!group_sync<0>(sm, half, group_phase)) return;
             // rescale factors of this tile go to the accumulate warps through an 8-deep ring (the softmax
             // warps can be at most five tiles ahead of the tile being drained)
             float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (gt & 7u) * 16u;
@@ -979,7 +1039,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 mbar_arrive(sm.bar(kBarRescale + (gt & 7u)));
             }
             // the O product that read this P buffer two tiles ago must be complete before it is rewritten
-            if (gt >= 2u && !wait_phase(sm, kBarOFull + buf, ph ^ 1u)) return;
+            if (gt >= 2u && !wait_phase<0>(sm, kBarOFull + buf, ph ^ 1u)) return;
             uint32_t *pdst = reinterpret_cast<uint32_t *>(sm.ptr + kSmP + buf * 2048u + key * 16u);
             const uint32_t c_hi = pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), c_lo = pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]);
             pdst[half] = c_hi;
@@ -996,9 +1056,9 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
         // denominators: sum the per-thread partial sums, hand (m, l) to the accumulate warps
         {
             const float wsum = warp_reduce4<false>(l, lane);
-            if (!group_sync(sm, half, group_phase)) return;   // everyone is past the last tile's reads of `red`
+            if (!group_sync<0>(sm, half, group_phase)) return;   // everyone is past the last tile's reads of `red`
             if ((lane & 7u) == 0) red[warp * 4u + (lane >> 3)] = wsum;
-            if (!group_sync(sm, half, group_phase)) return;
+            if (!group_sync<0>(sm, half, group_phase)) return;
             if (key == 0) {
                 float *fin = reinterpret_cast<float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
 #pragma unroll
@@ -1071,7 +1131,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
             const uint32_t buf = gt & 1u, ph = (gt >> 1) & 1u, slot = gt & 7u;
-            if (!wait_phase(sm, kBarRescale + slot, (gt >> 3) & 1u)) return;
+            if (!wait_phase<1>(sm, kBarRescale + slot, (gt >> 3) & 1u)) return;
             const float4 *ring = reinterpret_cast<const float4 *>(sm.ptr + kSmRescale + slot * 64u);
             const float4 ra = ring[0], rb = ring[1];
             const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
@@ -1085,7 +1145,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
                     for (int h = 0; h < 8; ++h) acc[mb][h] = __fmul_rn(acc[mb][h], r[h]);
             }
-            if (!wait_phase(sm, kBarOFull + buf, ph)) return;
+            if (!wait_phase<1>(sm, kBarOFull + buf, ph)) return;
             tc_fence_after();
 #pragma unroll
             for (uint32_t half = 0; half < 2; ++half) {        // two channel blocks at a time keeps registers in budget
@@ -1116,7 +1176,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         }
 
         // final (m, l) of this item from the softmax warps
-        if (!wait_phase(sm, kBarItemDone + (k & 7u), (k >> 3) & 1u)) return;
+        if (!wait_phase<1>(sm, kBarItemDone + (k & 7u), (k >> 3) & 1u)) return;
         const float *fin = reinterpret_cast<const float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u;
 
         __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.out) + (uint64_t)it.token * 4096u;
@@ -1145,9 +1205,9 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
             for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + ch] = acc[mb][h];
         if (ch < 16) mine[4096 + ch] = fin[ch];
         __threadfence();
-        if (!group_sync(sm, 3, group_phase)) return;
+        if (!group_sync<1>(sm, 3, group_phase)) return;
         if (ch == 0) misc[3] = atomicAdd(tickets + it.token, 1u);
-        if (!group_sync(sm, 3, group_phase)) return;
+        if (!group_sync<1>(sm, 3, group_phase)) return;
         const uint32_t ticket = misc[3];
         if (ticket + 1u == it.nparts) {
             __threadfence();
@@ -1243,25 +1303,35 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
     const uint32_t first = cta_first[blockIdx.x], end = cta_first[blockIdx.x + 1];
 
+    // Roles by warpgroup (four warps, one per SM sub-partition); the register file is re-divided
+    // first: the groups that need few registers release them before the others grow.
     if (warp < 8) {
+        if (kRegsSoftmax > kRegsLaunch) registers_acquire<kRegsSoftmax>();
         softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, first, end, tmem);
     } else if (warp < kWarpProducer) {
+        registers_acquire<kRegsAccumulate>();
         accumulate_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
-    } else if (warp < kWarpMma) {
+    } else if (warp < kWarpMma || warp >= kWarpProducerB) {
+        registers_release<kRegsProducer>();
         if (TMA && lane == 0) {
             tma_prefetch_descriptor(&ori_map);
             tma_prefetch_descriptor(RATIO == 128 ? &cmp_page_map : &cmp_map);
         }
-        producer_loop<RATIO, TMA>(p, sm, items, first, end, warp - kWarpProducer, lane, &ori_map, &cmp_map, &cmp_page_map);
+        const uint32_t set = warp >= kWarpProducerB ? 1u : 0u;
+        producer_loop<RATIO, TMA>(p, sm, items, first, end, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
+                                  &cmp_page_map);
         cp_async_wait<0>();
-    } else if (warp < kWarpQuery) {
-        if (lane == 0) {
+    } else {
+        if (kRegsIssue < kRegsLaunch) registers_release<kRegsIssue>();
+        if (warp >= kWarpQuery) {
+            query_loop<DEBUG>(p, dbg, sm, items, first, end, warp - kWarpQuery, lane);
+        } else {
+            // the whole warp runs the issue loop and one elected lane issues: with converged control
+            // flow the operand descriptors live in uniform registers, which halves the cost per MMA
             if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
             else mma_pv_loop(sm, cta_first, items, first, end, tmem);
+            __syncwarp();
         }
-        __syncwarp();
-    } else {
-        query_loop<DEBUG>(p, dbg, sm, items, first, end, warp - kWarpQuery, lane);
     }
 #ifdef SHAREDKV_TIMING
     timing_add(49, clock64() - kernel_start);
@@ -1382,7 +1452,7 @@ extern "C" __attribute__((visibility("default"))) int sharedkv_timing_read(unsig
 {
     cudaError_t e = cudaMemcpyFromSymbol(host, g_wait_cycles, sizeof(g_wait_cycles));
     if (e == cudaSuccess && reset) {
-        static unsigned long long zeros[kMaxCtas][400];
+        static unsigned long long zeros[kMaxCtas][450];
         e = cudaMemcpyToSymbol(g_wait_cycles, zeros, sizeof(zeros));
     }
     return (int)e;

@@ -112,6 +112,20 @@ __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t column
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(columns)
                  : "memory");
 }
+// Register file re-partitioning between warpgroups (four consecutive warps, all of which must
+// execute the instruction): a kernel launched with N registers per thread lets roles that need few
+// give registers up (dec) so that roles that need many can take them (inc, which waits until
+// they are free).  Counts are multiples of 8 in [24, 256].
+template <uint32_t COUNT>
+__device__ __forceinline__ void registers_release()
+{
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(COUNT));
+}
+template <uint32_t COUNT>
+__device__ __forceinline__ void registers_acquire()
+{
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(COUNT));
+}
 __device__ __forceinline__ void tmem_relinquish()
 {
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -149,6 +163,15 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4])
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(taddr)
                  : "memory");
+}
+
+// One lane of a fully converged warp.  The compiler keeps code predicated on this (unlike on a
+// lane-id comparison) on the warp-uniform datapath.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc], INT8 x INT8 -> INT32, one CTA.

@@ -86,7 +86,7 @@ def build_workload(args, rank, world):
             pairs -= 1
         if args.max_pairs:
             pairs = min(pairs, args.max_pairs)
-        ratios = [4, 128] * pairs
+        ratios = {"pair": [4, 128], "c4": [4], "c128": [128]}[args.layers] * pairs
         work = synthetic.build("box", device, mine, ratios=ratios, queries=1, seed=100 + rank, max_context=1 << 20)
         label = f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128"
     elif args.workload == "c128":
@@ -244,6 +244,8 @@ def main():
     parser.add_argument("--requests", type=int, default=2048)
     parser.add_argument("--kv-gb", type=float, default=150.0)
     parser.add_argument("--max-pairs", type=int, default=0)
+    parser.add_argument("--layers", default="pair", choices=("pair", "c4", "c128"),
+                        help="box workload: layer kinds per pair (one kind keeps a profiler capture small)")
     parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--no-e2e", action="store_true")
