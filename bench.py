@@ -66,6 +66,19 @@ def shard(lengths, ranks):
     return [sorted(o) for o in owner]
 
 
+def combine_ranks(elapsed_ms, counts, device, world):
+    """Whole-job figures from per-rank ones: the slowest rank's time, the sum of the work counts.
+    The only communication of the benchmark (the decode path itself has no exchange step)."""
+    if world <= 1:
+        return float(elapsed_ms), [float(c) for c in counts]
+    import torch.distributed as dist
+    times = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+    totals = torch.tensor(list(counts), dtype=torch.float64, device=device)
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    return float(times[0]), totals.tolist()
+
+
 def pair_bytes(lengths):
     """Resident bytes of one C4 + C128 layer pair (compressed pools dominate)."""
     c4 = ((lengths // 4 + 31) // 32).clamp_min(1).sum() * 16384
@@ -112,7 +125,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
@@ -237,7 +250,7 @@ def run_reference(args, rank, world):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=("b200", "reference"))
     parser.add_argument("--workload", default="box", choices=("box", "c128", "c4mtp"))
@@ -307,14 +320,10 @@ def main():
         ratio = work.layers[layer].ratio
         entry = per_kind.setdefault(ratio, [0.0, 0, 0])
         entry[0] += a.elapsed_time(b); entry[1] += 1; entry[2] += rows_per_layer[layer]
-    times = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
-    counts = torch.tensor([queries_per_step * args.steps, sum(rows_per_layer[l] for l, _, _ in marks)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        dist.all_reduce(counts, op=dist.ReduceOp.SUM)
-    total_ms = float(times[0])
-    value = float(counts[0]) / (total_ms / 1000)
-    kv_gbs = float(counts[1]) * ROW_BYTES / 1e9 / (total_ms / 1000)
+    total_ms, counts = combine_ranks(elapsed_ms, [queries_per_step * args.steps, sum(rows_per_layer[l] for l, _, _ in marks)],
+                                     device, world)
+    value = counts[0] / (total_ms / 1000)
+    kv_gbs = counts[1] * ROW_BYTES / 1e9 / (total_ms / 1000)
 
     # ---- end to end through the prepared operators with host buffers
     e2e = None
@@ -324,33 +333,53 @@ def main():
         host_rows = torch.randn(tokens, 512).bfloat16().pin_memory()
         host_out = [torch.empty(tokens, 8, 512, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         host_idx = None
-        dev_rows = torch.empty(tokens, 512, dtype=torch.bfloat16, device=device)
         # the new token of request b lands in the last row of its window: logical row seq_len - 1
         last = (work.seq_lens_host - 1)
         slot_pages = work.ori_table[torch.arange(work.requests, device=device), (last // 32).to(device)].long()
         slots = (slot_pages * 32 + (last % 32).to(device)).to(torch.int32).repeat_interleave(work.queries)
-        writers, h2d, d2h = [], 0, 0
+        writers, dev_rows, h2d, d2h = [], [], 0, 0
         for i in range(layers):
             layer = work.layers[i]
             inverse = layer.ori_scale.double().reciprocal().float()
-            writers.append(PreparedCacheWrite(layer.ori, dev_rows, slots, inverse))
+            dev_rows.append(torch.empty(tokens, 512, dtype=torch.bfloat16, device=device))
+            writers.append(PreparedCacheWrite(layer.ori, dev_rows[i], slots, inverse))
             if layer.cmp_indices is not None and host_idx is None:
                 host_idx = layer.cmp_indices.cpu().pin_memory()
+        # Three streams: inputs of layer i + 1 cross PCIe while layer i computes and layer i - 1's
+        # output goes back.  Every layer owns its device-side Q, rows, indices and output, so the only
+        # ordering needed is copy-in -> compute -> copy-out per layer, and "the previous use of this
+        # layer's buffers is over" before they are overwritten.
         copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
         main_stream = torch.cuda.current_stream(device)
+        staged = [torch.cuda.Event() for _ in range(layers)]
+        computed = [torch.cuda.Event() for _ in range(layers)]
+        returned = [torch.cuda.Event() for _ in range(layers)]
+        used = [False] * layers
 
         def e2e_layer(i, slot):
             nonlocal h2d, d2h
             layer = work.layers[i]
-            layer.q.copy_(host_q[i % len(host_q)], non_blocking=True)
-            dev_rows.copy_(host_rows, non_blocking=True)
-            moved = layer.q.numel() * 2 + dev_rows.numel() * 2
-            if layer.cmp_indices is not None:
-                layer.cmp_indices.copy_(host_idx, non_blocking=True)
-                moved += host_idx.numel() * 4
+            with torch.cuda.stream(copy_in):
+                if used[i]:
+                    copy_in.wait_event(computed[i])
+                layer.q.copy_(host_q[i % len(host_q)], non_blocking=True)
+                dev_rows[i].copy_(host_rows, non_blocking=True)
+                moved = layer.q.numel() * 2 + dev_rows[i].numel() * 2
+                if layer.cmp_indices is not None:
+                    layer.cmp_indices.copy_(host_idx, non_blocking=True)
+                    moved += host_idx.numel() * 4
+                staged[i].record(copy_in)
+            main_stream.wait_event(staged[i])
+            if used[i]:
+                main_stream.wait_event(returned[i])       # the output of the previous step has been read
             writers[i].run()
             out = ops[i].run()
-            host_out[slot].copy_(out, non_blocking=True)
+            computed[i].record(main_stream)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(computed[i])
+                host_out[slot].copy_(out, non_blocking=True)
+                returned[i].record(copy_out)
+            used[i] = True
             h2d += moved
             d2h += out.numel() * 2
 
@@ -358,7 +387,7 @@ def main():
             which = sequence if sequence is not None else [index % layers]
             for n, i in enumerate(which):
                 e2e_layer(i, n & 1)
-            torch.cuda.current_stream(device).synchronize()
+            main_stream.wait_stream(copy_out)             # the step ends when its last result is on the host
 
         for i in range(3):
             e2e_step(i)
@@ -372,12 +401,10 @@ def main():
         t1.record()
         barrier()
         wall = time.perf_counter() - wall
-        e2e_ms = torch.tensor([max(t0.elapsed_time(t1), 0.0)], dtype=torch.float64, device=device)
-        if world > 1:
-            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-        e2e = {"value": float(counts[0]) / (float(e2e_ms[0]) / 1000), "unit": "queries/s",
+        e2e_ms, _ = combine_ranks(max(t0.elapsed_time(t1), 0.0), [0], device, world)
+        e2e = {"value": counts[0] / (e2e_ms / 1000), "unit": "queries/s",
                "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
-               "ms_per_step": float(e2e_ms[0]) / args.steps}
+               "ms_per_step": e2e_ms / args.steps}
 
     if rank != 0:
         if world > 1:

@@ -128,3 +128,41 @@ def test_request_sharding_is_balanced_and_complete():
         assert sorted(i for s in shards for i in s) == list(range(2048))
         loads = [int((lengths[torch.tensor(s)] // 4 + lengths[torch.tensor(s)] // 128 + 256).sum()) for s in shards]
         assert max(loads) <= 1.02 * (sum(loads) / ranks)
+
+
+def _two_rank_worker(rank, world, port, results):
+    import torch.distributed as dist
+    import bench
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        lengths = bench.box_lengths(256, seed=0)
+        mine = bench.shard(lengths, world)[rank]
+        # every rank derives the same partition on its own: no exchange is needed to agree on it
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        cost = int((lengths[torch.tensor(mine)] // 4 + lengths[torch.tensor(mine)] // 128 + 256).sum())
+        total_ms, counts = bench.combine_ranks(10.0 + rank, [len(mine), cost], torch.device("cpu"), world)
+        results[rank] = (gathered, total_ms, counts, cost)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_shard_requests_and_combine_timings():
+    """World size 2 on the gloo backend: the ranks' request shards are disjoint, complete and
+    balanced, and the whole-job figures are the slowest rank's time and the summed counts."""
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_two_rank_worker, args=(2, port, results), nprocs=2, join=True)
+    assert set(results.keys()) == {0, 1}
+    gathered, total_ms, counts, _ = results[0]
+    assert results[1][0] == gathered
+    assert sorted(gathered[0] + gathered[1]) == list(range(256)) and not set(gathered[0]) & set(gathered[1])
+    assert total_ms == 11.0 and results[1][1] == 11.0
+    assert counts[0] == 256 and counts[1] == results[0][3] + results[1][3]
+    costs = [results[0][3], results[1][3]]
+    assert max(costs) / min(costs) < 1.02

@@ -1,0 +1,126 @@
+"""Serving-shaped checks of the decode path on the GPU.
+
+* CUDA-graph replay with a live batch that changes between replays (the reference's
+  tests/npu/test_dynamic.py:33-65): the live shape is derived on the device at every replay and
+  rows past it are zeroed.
+* Workload-sized parity: a synthetic serving batch (contexts up to 1M tokens, both layer kinds)
+  is run on the GPU; sampled requests are extracted as small CPU cases and compared with the
+  oracle inside the acceptance band (max-abs 2e-2, mean-abs 2e-3); the whole batch is checked
+  through two size-independent properties: bit-identical repeat launches, and bit-identical
+  output when Q is doubled and the softmax scale halved (the query's absmax scale doubles
+  exactly, so codes and logits do not change).
+"""
+from dataclasses import replace
+
+import pytest
+import torch
+
+from oracle import sharedkv_oracle as oracle
+from tests.support import bf16, error_metrics, load_case, to_device
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda:0"
+
+
+def prepared(case, ori_scale, cmp_scale, **kw):
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    return PreparedAttention(case, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), **kw)
+
+
+@pytest.mark.parametrize("name", ("config0_c4", "mixed_c128"))
+def test_graph_replay_follows_the_live_batch(name):
+    case, ori_scale, cmp_scale, z = load_case(name)
+    dev = to_device(case, DEVICE)
+    op = prepared(dev, ori_scale, cmp_scale, return_lse=True)
+    expected, expected_lse = bf16(z["out_s1"]).float(), torch.from_numpy(z["lse_s1"])
+    batch = case.seq_lens.numel()
+    assert batch >= 2
+    boundaries = case.cu_q.tolist()
+
+    op.run()                                     # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream(device=DEVICE)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            op.run()
+    torch.cuda.synchronize()
+
+    full_lens, full_cu = dev.seq_lens.clone(), dev.cu_q.clone()
+    for live in (batch, batch - 1, batch):
+        dev.seq_lens.copy_(full_lens)
+        dev.cu_q.copy_(full_cu)
+        if live < batch:                         # trailing requests become padding
+            dev.seq_lens[live:] = 0
+            dev.cu_q[live + 1:] = -1
+        op.out.fill_(3.0)
+        op.lse.fill_(3.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        tokens = boundaries[live]
+        out, lse = op.out.cpu().float(), op.lse.cpu()
+        m = error_metrics(out[:tokens], expected[:tokens])
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, (live, m)
+        torch.testing.assert_close(lse[:tokens], expected_lse[:tokens], rtol=2e-5, atol=2e-5)
+        assert not out[tokens:].any() and not lse[tokens:].any(), live      # padded rows are cleared
+
+
+def test_an_all_padding_batch_writes_zeros():
+    case, ori_scale, cmp_scale, _ = load_case("config0_c4")
+    dev = to_device(case, DEVICE)
+    op = prepared(dev, ori_scale, cmp_scale, return_lse=True)
+    dev.seq_lens.zero_()
+    op.out.fill_(5.0)
+    op.lse.fill_(5.0)
+    op.run()
+    torch.cuda.synchronize()
+    assert not op.out.any() and not op.lse.any()
+
+
+@pytest.fixture(scope="module")
+def serving_batch():
+    from npu_sparse_attn_sharedkv_int8 import synthetic
+    lengths = synthetic.log_uniform_lengths(160, 4096, 1 << 20, seed=7)
+    lengths[0], lengths[1], lengths[2] = 1 << 20, 4096, 4099          # the extremes are always present
+    work = synthetic.build("box", DEVICE, lengths, ratios=[4, 128], seed=11, max_context=1 << 20)
+    yield work
+    del work
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("layer_index", (0, 1))
+def test_serving_batch_against_the_oracle_and_its_invariants(serving_batch, layer_index):
+    from npu_sparse_attn_sharedkv_int8 import synthetic
+    work = serving_batch
+    layer = work.layers[layer_index]
+    case = work.case(layer_index)
+    op = prepared(case, layer.ori_scale, layer.cmp_scale, return_lse=True)
+    out = op.run().clone()
+    lse = op.lse.clone()
+    torch.cuda.synchronize()
+
+    # sampled requests against the CPU oracle (longest, shortest and a spread in between)
+    order = torch.argsort(work.seq_lens_host).tolist()
+    sample = sorted({order[0], order[1], order[len(order) // 3], order[len(order) // 2], order[-2], order[-1], 0, 1, 2})
+    small, ori_scale, cmp_scale, ids = synthetic.extract_requests(work, layer_index, sample)
+    expected, expected_lse = oracle.attention_tiled(small, ori_scale, cmp_scale, return_lse=True)
+    m = error_metrics(out[ids.to(DEVICE)].cpu().float(), expected.float())
+    assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+    torch.testing.assert_close(lse[ids.to(DEVICE)].cpu(), expected_lse, rtol=1e-4, atol=1e-4)
+
+    # repeat launches are bit-identical (the split-K merge order is fixed by piece number)
+    again = op.run()
+    torch.cuda.synchronize()
+    assert torch.equal(again, out)
+
+    # Q * 2 with softmax_scale / 2: the same codes, the same logits, the same bits
+    doubled = replace(case, q=(case.q.float() * 2).bfloat16(), softmax_scale=case.softmax_scale / 2)
+    twin = prepared(doubled, layer.ori_scale, layer.cmp_scale, return_lse=True)
+    assert torch.equal(twin.run(), out)
+    torch.cuda.synchronize()
+    assert torch.equal(twin.lse, lse)
+
+    # every output row is a convex combination of dequantised rows plus the sink's share: finite, bounded
+    bound = float((127 * torch.maximum(layer.ori_scale, layer.cmp_scale)).max())
+    assert torch.isfinite(out.float()).all() and float(out.float().abs().max()) <= bound * 1.01
