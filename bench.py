@@ -1,6 +1,6 @@
 """Benchmark of the INT8 shared-KV decode path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload box|c128|c4mtp]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload box|c128|c4mtp|writer]
 
 Default workload ("box"): the box-scale decode step.  2048 concurrent requests with context
 lengths log-uniform over 4k..1M tokens are batch-sharded over the N GPUs (longest-first
@@ -14,8 +14,11 @@ Printed JSON line (rank 0): `value` = (request, layer) attention evaluations per
 over all GPUs with everything resident in HBM; `e2e` = the same through the prepared
 operators with host buffers: per step and layer the new KV row of every request, Q and
 (C4) the top-k selections are copied from pinned host memory, the cache writer and the
-attention run, and the BF16 output is copied back.  `roofline` is for the dominant kernel
-(the C4 decode launch): algorithmic KV bytes per launch over its mean CUDA-event duration.
+attention run, and the BF16 output is copied back (three streams, so copies overlap compute).
+`roofline` is for the layer kind with the larger share of the step (`roofline_other` for the
+other): algorithmic KV bytes per launch over its mean CUDA-event duration, plan kernel included.
+`--workload writer` times the paged cache writer instead (65 536 rows into the original cache and
+16 384 into the ratio-4 compressed cache per step) and prints rows/s.
 `--impl reference` times the CPU restatement of the reference's Python path (the reference
 itself is Python and does not travel to the GPU box) on a bounded seeded sample.
 """
@@ -38,6 +41,9 @@ import torch  # noqa: E402
 
 METRIC = "decode attn queries/s/GPU & achieved HBM GB/s (INT8 KV) at 1/2/4/8 B200"
 ROW_BYTES = 512
+# DRAM traffic (read + written) per algorithmic KV byte, from ncu captures of smaller launches of the
+# same kernels (profiles/decode_kernel_*.md); traffic grows in proportion to the queries processed.
+TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.076, 128: 1.036}
 
 
 def measured_peaks():
@@ -87,6 +93,14 @@ def pair_bytes(lengths):
     return int(c4 + c128 + ori)
 
 
+def workload_label(args):
+    return {"box": f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128",
+            "c128": "C128 decode, B=64, T=1, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)",
+            "c4mtp": "C4 decode with MTP, B=256, T=2, ctx U[32k,128k], top-k 1024 + window 128",
+            "writer": "paged INT8 cache writer: 65536 BF16 rows -> original cache + 16384 rows -> ratio-4 compressed cache, random slots"
+            }[args.workload]
+
+
 def build_workload(args, rank, world):
     from npu_sparse_attn_sharedkv_int8 import synthetic
     device = torch.device("cuda", torch.cuda.current_device())
@@ -101,19 +115,16 @@ def build_workload(args, rank, world):
             pairs = min(pairs, args.max_pairs)
         ratios = {"pair": [4, 128], "c4": [4], "c128": [128]}[args.layers] * pairs
         work = synthetic.build("box", device, mine, ratios=ratios, queries=1, seed=100 + rank, max_context=1 << 20)
-        label = f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128"
     elif args.workload == "c128":
         lengths = synthetic.uniform_lengths(64, 8192, 131072, seed=1)
         ratios = [128] * args.rotate
         work = synthetic.build("c128", device, lengths, ratios=ratios, queries=1, seed=200 + rank, stride_slots=38,
                                slot_offset=1, max_context=135000)
-        label = "C128 decode, B=64, T=1, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)"
     else:
         lengths = synthetic.uniform_lengths(256, 32768, 131072, seed=2)
         ratios = [4] * args.rotate
         work = synthetic.build("c4mtp", device, lengths, ratios=ratios, queries=2, seed=300 + rank, max_context=135000)
-        label = "C4 decode with MTP, B=256, T=2, ctx U[32k,128k], top-k 1024 + window 128"
-    return work, label
+    return work, workload_label(args)
 
 
 # --------------------------------------------------------------------------- clocks
@@ -211,6 +222,118 @@ def time_cpu_path(lengths, ratios, budget_s, threads):
     return done / spent, rows / spent, done
 
 
+# --------------------------------------------------------------------------- cache writer
+WRITER_METRIC = "paged INT8 KV cache writer rows/s & achieved HBM GB/s (BF16 -> INT8 quantize + slot scatter)"
+WRITER_ROWS = ((65536, 1), (16384, 4))          # (rows per step, cache ratio): original cache, ratio-4 compressed cache
+
+
+def writer_inputs(rows, seed, device):
+    """Rows ~ N(0, sigma_c^2) with lognormal per-channel sigma, frozen scale 1.1 absmax / 127,
+    a cache of rows/32 + 25 % pages and distinct random slots."""
+    g = torch.Generator().manual_seed(seed)
+    sigma = torch.exp(0.5 * torch.randn(512, generator=g))
+    updates = (torch.randn(rows, 512, generator=g) * sigma).bfloat16()
+    scale = (1.1 * updates.float().abs().amax(0) / 127).clamp_min(1e-6)
+    pages = rows // 32 + rows // 128
+    slots = torch.randperm(pages * 32, generator=g)[:rows].to(torch.int32)
+    inverse = scale.double().reciprocal().float()
+    return updates.to(device), slots.to(device), inverse.to(device), pages, scale
+
+
+def run_writer(args, rank, world, local):
+    from npu_sparse_attn_sharedkv_int8 import PreparedCacheWrite
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    copies = max(2, args.rotate)              # each launch touches buffers the previous `copies - 1` did not: > L2 in all
+    ops, host_sets = [], []
+    for c in range(copies):
+        for rows, ratio in WRITER_ROWS:
+            updates, slots, inverse, pages, scale = writer_inputs(rows, 1000 * rank + 10 * c + ratio, device)
+            cache = torch.zeros(pages, 32, 1, 512, dtype=torch.int8, device=device)
+            ops.append((PreparedCacheWrite(cache, updates, slots, inverse), rows))
+            if c == 0:
+                host_sets.append((updates.cpu().pin_memory(), slots.cpu().pin_memory(), updates, slots, scale))
+    per_step = len(WRITER_ROWS)
+
+    def step(i):
+        for k in range(per_step):
+            ops[(i % copies) * per_step + k][0].run()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for i in range(args.steps):
+        step(i)
+    finish.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    rows_per_step = sum(r for r, _ in WRITER_ROWS)
+    total_ms, counts = combine_ranks(begin.elapsed_time(finish), [rows_per_step * args.steps], device, world)
+    value = counts[0] / (total_ms / 1000)
+
+    # end to end: rows and slots come from pinned host memory every step; a 64-byte probe of the cache goes back
+    probe = torch.empty(64, dtype=torch.int8).pin_memory()
+    def e2e_step():
+        for k, (host_rows, host_slots, dev_rows, dev_slots, _) in enumerate(host_sets):
+            dev_rows.copy_(host_rows, non_blocking=True)
+            dev_slots.copy_(host_slots, non_blocking=True)
+            ops[k][0].run()
+        probe.copy_(ops[0][0].cache.view(-1)[:64], non_blocking=True)
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    t1.record()
+    barrier()
+    e2e_ms, _ = combine_ranks(t0.elapsed_time(t1), [0], device, world)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    from oracle import sharedkv_oracle as oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    host_rows, host_slots, _, _, scale = host_sets[0]
+    cpu_cache = torch.zeros(ops[0][0].cache.shape, dtype=torch.int8)
+    cpu_rows, spent = 0, 0.0
+    while spent < max(args.cpu_seconds, 0.5):
+        start = time.perf_counter()
+        oracle.write_cache(cpu_cache, host_rows[:8192], host_slots[:8192].long(), scale.double().reciprocal().float())
+        spent += time.perf_counter() - start
+        cpu_rows += 8192
+    peak, peak_kind = measured_peaks()
+    achieved = value / world * 1536 / 1e9
+    print(json.dumps({
+        "metric": WRITER_METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": workload_label(args), "rows_per_step_per_gpu": rows_per_step,
+                   "l2": f"rotating {copies} sets of rows and caches ({copies * rows_per_step * 1536 / 1e6:.0f} MB) so no launch finds its data in L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_kind, "ms_per_launch": total_ms / args.steps / per_step,
+                     "algorithmic_bytes_per_launch": rows_per_step * 1536 // per_step, "kernel": "cache_write_kernel"},
+        "cpu_baseline": {"value": cpu_rows / spent, "unit": "rows/s", "cores": os.cpu_count() or 1, "kind": "port",
+                         "sample": f"{cpu_rows} rows in calls of 8192"},
+        "e2e": {"value": counts[0] / (e2e_ms / 1000), "unit": "rows/s",
+                "h2d_bytes_per_step": sum(h.numel() * 2 + sl.numel() * 4 for h, sl, _, _, _ in host_sets), "d2h_bytes_per_step": 64},
+        "gpu_launches": per_step * args.steps, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- main
 def run_reference(args, rank, world):
     if rank != 0:
@@ -225,7 +348,7 @@ def run_reference(args, rank, world):
         lengths, ratios = uniform_lengths(256, 32768, 131072, seed=2), [4]
     else:
         ratios = [4, 128]
-    per_step = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    per_step = max(0.25, min(20.0, 120.0 / max(1, args.steps + args.warmup)))      # about two minutes in all
     for _ in range(args.warmup):
         time_cpu_path(lengths, ratios, per_step / 4, threads)
     rates, row_rates, counted = [], [], 0
@@ -240,7 +363,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * elapsed / max(1, args.steps),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": args.workload, "requests": args.requests},
+        "config": {"workload": workload_label(args), "requests": args.requests},
         "kv_gbs": statistics.mean(row_rates) * ROW_BYTES / 1e9,
         "cpu_baseline": {"value": value, "unit": "queries/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -253,7 +376,7 @@ def main():
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=("b200", "reference"))
-    parser.add_argument("--workload", default="box", choices=("box", "c128", "c4mtp"))
+    parser.add_argument("--workload", default="box", choices=("box", "c128", "c4mtp", "writer"))
     parser.add_argument("--requests", type=int, default=2048)
     parser.add_argument("--kv-gb", type=float, default=150.0)
     parser.add_argument("--max-pairs", type=int, default=0)
@@ -270,6 +393,9 @@ def main():
         return
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "writer":
+        run_writer(args, rank, world, local)
+        return
 
     import torch.distributed as dist
     from npu_sparse_attn_sharedkv_int8 import PreparedAttention, PreparedCacheWrite
@@ -415,7 +541,9 @@ def main():
     for ratio, (ms, launches, rows) in per_kind.items():
         achieved = rows * ROW_BYTES / 1e9 / (ms / 1000)
         roof[ratio] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                       "traffic": None, "peak_source": peak_kind, "ms_per_launch": ms / launches,
+                       "traffic": int(TRAFFIC_PER_ALGORITHMIC_BYTE[ratio] * rows * ROW_BYTES // launches),
+                       "traffic_source": "ncu capture of a smaller launch, scaled by algorithmic bytes",
+                       "peak_source": peak_kind, "ms_per_launch": ms / launches,
                        "algorithmic_bytes_per_launch": rows * ROW_BYTES // launches, "launches": launches}
     dominant = max(per_kind, key=lambda r: per_kind[r][0])
     cpu_qps, cpu_rows, cpu_n = time_cpu_path(work.seq_lens_host, [l.ratio for l in work.layers], args.cpu_seconds,
