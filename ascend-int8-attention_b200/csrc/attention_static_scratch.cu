@@ -10,9 +10,10 @@
 // for the workspace field.
 //
 // Consequences of the array being shared by every call on a device:
-//  * Nothing in it has to start at zero and nothing is carried from one call to the next: the plan
-//    kernel that runs in front of every decode kernel rewrites the header, the item list and the
-//    tickets, and a partial state is always written before it is read.
+//  * The caller never has to clear it and nothing is carried from one call to the next: every call
+//    itself zeroes the part that must start at zero (split-K tickets, status word) on the stream
+//    in front of its kernel, the kernel rebuilds the work plan, and a partial state is always
+//    written before it is read.
 //  * Two calls that are in flight at the same time on one device (two streams, two threads, two
 //    branches of a graph) use the same bytes and corrupt each other.  Calls issued to one stream
 //    run one after the other and are safe.  Callers that need concurrency use the regular entry

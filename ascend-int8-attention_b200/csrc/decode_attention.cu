@@ -1,29 +1,30 @@
 // INT8 shared-KV decode attention for sm_100a (C4: top-k compressed rows + window,
 // C128: every compressed row + window), eight heads, D = 512.
 //
-// Two launches per call, both on the caller's stream:
+// One call = a memset of the small plan area of the workspace (split-K tickets, status word) and
+// one kernel launch, both on the caller's stream.
 //
-//   plan_kernel    one CTA.  Derives the live batch / token count from cuQ and seqLens
-//                  (trailing requests with seqLens <= 0 or cuQ < 0 are padding, as in the
-//                  reference's device code csrc/kernels/c8/attention_impl.h:121-137), counts
-//                  the 128-key tiles of every query token, cuts the flat tile list into one
-//                  contiguous range per CTA and writes the resulting work items, the per-CTA
-//                  item ranges and zeroed merge tickets into the workspace.
-//
-//   decode_kernel  one persistent CTA per SM, 9 warps:
-//                    warps 0-3  softmax / accumulate (thread = key for scores, = channel for outputs)
-//                    warps 4-7  producers: page-table lookups + 16-byte cp.async row gathers into a
-//                               3-stage ring of 128-key x 512-byte tiles (128-byte swizzled)
-//                    warp  8    one thread issues tcgen05.mma kind::i8 and commits to mbarriers
-//                  Per tile:  S[128 keys,16] = KV[128,512] . Qcodes[16,512]^T   (16 MMAs, K-major operands)
-//                             softmax in FP32 registers, P codes [128 keys,16] to shared memory
-//                             O[512,16]     = KV^T[512,128] . P[128,16]         (16 MMAs, MN-major operands;
-//                                             the SAME shared-memory tile serves both products)
-//                  Columns 0-7 of S / O belong to the high code plane of Q / P, 8-15 to the low
-//                  (residual) plane.  INT32 accumulators live in tensor memory and are converted to
-//                  FP32 once per tile, exactly as the CPU reference does per tile.
-//                  A token whose tiles span several CTAs is merged by the last CTA to finish a piece
-//                  (atomic ticket; nobody waits for another CTA).
+//   decode_kernel  one persistent CTA per SM, 24 warps in six roles that meet only at mbarriers.
+//     set-up       every CTA derives the live batch / token count from cuQ and seqLens (trailing
+//                  requests with seqLens <= 0 or cuQ < 0 are padding, as in the reference's device
+//                  code csrc/kernels/c8/attention_impl.h:121-137), counts the 128-key tiles of
+//                  every query token, cuts the flat tile list into one contiguous range per CTA
+//                  and writes its own work items into the workspace (plan_cta).
+//     warps 12-15, 20-23  producers (even / odd tiles): row selection -> page table -> row id, two
+//                  tiles ahead; rows land in a 3-stage ring of 128-key x 512-byte tiles (128-byte
+//                  swizzle) by TMA row gathers (whole-page boxes for C128 compressed rows, 16-byte
+//                  cp.async when the page strides rule TMA out)
+//     warps 18-19  query encode: fold scale, absmax, hi / lo INT8 planes of the next item
+//     warp  16     S[128 keys,16] = KV[128,512] . Qcodes[16,512]^T   16 x tcgen05.mma kind::i8, K-major
+//     warps 0-7    softmax in FP32 registers, P codes [128 keys,16] to shared memory
+//     warp  17     O[512,16] = KV^T[512,128] . P[128,16]             16 MMAs, MN-major operands: the
+//                  SAME shared-memory tile serves both products
+//     warps 8-11   accumulate: INT32 O -> FP32 running sums, finalise / split-K partials / merge
+//   Columns 0-7 of S / O belong to the high code plane of Q / P, 8-15 to the low (residual) plane.
+//   INT32 accumulators live in tensor memory (S and O double-buffered) and are converted to FP32
+//   once per tile, exactly as the CPU reference does per tile.  A token whose tiles span several
+//   CTAs is merged by the last CTA to finish a piece (atomic ticket; nobody waits for another CTA).
+//   Registers are re-divided between the roles at kernel start (setmaxnreg).
 //
 // Arithmetic contract (npu_sparse_attn_sharedkv_int8/reference.py:268-322 of the reference):
 //   f = float(q) * scale_kind;  alpha = max(max|f| * (1/127), 1e-12);  n = clamp(f * (1/alpha), +-127)
@@ -79,7 +80,6 @@ static_assert(2 * kRegsSoftmax + kRegsAccumulate + 2 * kRegsProducer + kRegsIssu
 static_assert(kRegsSoftmax >= kRegsLaunch && kRegsAccumulate >= kRegsLaunch && kRegsProducer <= kRegsLaunch && kRegsIssue <= kRegsLaunch,
               "acquire only grows, release only shrinks");
 constexpr uint32_t kMaxCtas = 160;
-constexpr uint32_t kPlanThreads = 1024;
 constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
 constexpr float kInv127 = (float)(1.0 / 127);
 constexpr float kMasked = -1e30f;
@@ -151,7 +151,7 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lan
     return v;
 }
 
-// Exclusive prefix over the 1024 threads of the plan CTA; `total` receives the sum.
+// Exclusive prefix over the threads of the CTA (up to 1024); `total` receives the sum.
 __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *scratch, uint32_t &total)
 {
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
@@ -159,7 +159,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
     if (lane == 31) scratch[warp] = incl;
     __syncthreads();
     if (warp == 0) {
-        const uint32_t s = scratch[lane];
+        const uint32_t s = lane < (blockDim.x >> 5) ? scratch[lane] : 0u;
         const uint32_t si = warp_inclusive_scan(s, lane);
         scratch[32 + lane] = si - s;
         if (lane == 31) scratch[64] = si;
@@ -185,102 +185,110 @@ __device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_ba
     return lo;
 }
 
+// Work split, computed by every CTA for itself at the start of the decode kernel (all threads take
+// part).  The live shape comes from cuQ / seqLens on the device, so a captured graph follows the
+// live batch.  Every live token has 1 + ceil(compressed rows / 128) tiles; the flat tile list is cut
+// into `grid` equal ranges; the pieces of tokens that fall into this CTA's range become its items,
+// written to the workspace at the positions they have in the global item order (so that two CTAs
+// never write the same entry).  `scratch` is shared memory the roles do not use yet (the KV ring).
+struct PlanResult {
+    uint32_t first, end, live_tokens;
+};
+struct PlanScratch {
+    uint32_t scan[80];
+    uint32_t live, mismatch, first, count;
+    int32_t cu[kPlanStaged];
+};
 template <int RATIO>
-__global__ void __launch_bounds__(kPlanThreads) plan_kernel(const SharedKVArgs p, const uint32_t grid)
+__device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch *sc)
 {
-    __shared__ uint32_t scratch[80];
-    __shared__ uint32_t s_live, s_mismatch;
-    __shared__ int32_t s_cu[kPlanStaged];
     const uint32_t tid = threadIdx.x;
     const int32_t *cu_global = reinterpret_cast<const int32_t *>(p.cuQ);
     const int32_t *seq = reinterpret_cast<const int32_t *>(p.seqLens);
     char *ws = reinterpret_cast<char *>(p.workspace);
-    PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
-    uint32_t *cta_first = reinterpret_cast<uint32_t *>(ws + kWsCtaFirst);
     Item *items = reinterpret_cast<Item *>(ws + kWsItems);
-    uint32_t *tile_start = reinterpret_cast<uint32_t *>(ws + ws_tile_start(p.tokens));
-    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
 
-    if (tid == 0) { s_live = 0; s_mismatch = 0xffffffffu; }
+    if (tid == 0) { sc->live = 0; sc->mismatch = 0xffffffffu; sc->first = 0xffffffffu; sc->count = 0; }
     const bool staged = p.batch + 1u <= kPlanStaged;
     if (staged)
-        for (uint32_t b = tid; b <= p.batch; b += kPlanThreads) s_cu[b] = cu_global[b];
+        for (uint32_t b = tid; b <= p.batch; b += kThreads) sc->cu[b] = cu_global[b];
     __syncthreads();
-    const int32_t *cu = staged ? s_cu : cu_global;
+    const int32_t *cu = staged ? sc->cu : cu_global;
     uint32_t live = 0, mismatch = 0xffffffffu;
-    for (uint32_t b = tid; b < p.batch; b += kPlanThreads) {
+    for (uint32_t b = tid; b < p.batch; b += kThreads) {
         if (seq[b] > 0 && cu[b + 1] >= 0) live = b + 1;
         if (cu[b + 1] != (int32_t)(b + 1) && mismatch == 0xffffffffu) mismatch = b;
     }
-    if (live) atomicMax(&s_live, live);
-    if (mismatch != 0xffffffffu) atomicMin(&s_mismatch, mismatch);
+    if (live) atomicMax(&sc->live, live);
+    if (mismatch != 0xffffffffu) atomicMin(&sc->mismatch, mismatch);
     __syncthreads();
-    const uint32_t live_batch = s_live;
+    const uint32_t live_batch = sc->live;
     int32_t end = live_batch ? cu[live_batch] : 0;
     const uint32_t live_tokens = end <= 0 ? 0u : ((uint32_t)end < p.tokens ? (uint32_t)end : p.tokens);
     // one query token per request (plain decode): token t belongs to request t
-    const bool one_each = live_tokens == live_batch && cu[0] == 0 && s_mismatch >= live_batch;
+    const bool one_each = live_tokens == live_batch && cu[0] == 0 && sc->mismatch >= live_batch;
 
-    // pass 1: flat tile offset of every live token
-    uint32_t carry = 0;
-    for (uint32_t base = 0; base < live_tokens; base += kPlanThreads) {
-        const uint32_t t = base + tid;
-        uint32_t n = 0;
-        if (t < live_tokens) {
-            const uint32_t b = one_each ? t : owner_of(cu, live_batch, t);
-            const int32_t position = seq[b] - (cu[b + 1] - (int32_t)t);
-            n = tiles_of_token(RATIO, position, p.topk);
-        }
-        uint32_t total;
-        const uint32_t offset = block_exclusive_scan(n, scratch, total);
-        if (t < live_tokens) tile_start[t] = carry + offset;
-        carry += total;
+    // Thread i owns the consecutive tokens [i * per, (i + 1) * per): two block-wide scans in all,
+    // one of tiles (gives the quota per CTA) and one of pieces (gives the positions of the items).
+    const uint32_t per = (live_tokens + kThreads - 1) / kThreads;
+    const uint32_t t_begin = min(tid * per, live_tokens), t_end = min(t_begin + per, live_tokens);
+    auto tiles_of = [&](uint32_t t, uint32_t &batch, int32_t &position) {
+        batch = one_each ? t : owner_of(cu, live_batch, t);
+        position = seq[batch] - (cu[batch + 1] - (int32_t)t);
+        return tiles_of_token(RATIO, position, p.topk);
+    };
+    uint32_t my_tiles = 0;
+    for (uint32_t t = t_begin; t < t_end; ++t) {
+        uint32_t batch; int32_t position;
+        my_tiles += tiles_of(t, batch, position);
     }
-    const uint32_t total_tiles = carry;
+    uint32_t total_tiles;
+    const uint32_t tile_base = block_exclusive_scan(my_tiles, sc->scan, total_tiles);
     const uint32_t quota = total_tiles ? (total_tiles + grid - 1) / grid : 1;
-    for (uint32_t c = tid; c <= grid; c += kPlanThreads) cta_first[c] = 0xffffffffu;
-    __syncthreads();
+    const uint32_t me = blockIdx.x;
 
-    // pass 2: cut tokens at CTA boundaries and emit items
-    uint32_t item_carry = 0;
-    for (uint32_t base = 0; base < live_tokens; base += kPlanThreads) {
-        const uint32_t t = base + tid;
-        uint32_t pieces = 0, start = 0, n = 0, batch = 0;
-        int32_t position = 0;
-        if (t < live_tokens) {
-            batch = one_each ? t : owner_of(cu, live_batch, t);
-            position = seq[batch] - (cu[batch + 1] - (int32_t)t);
-            n = tiles_of_token(RATIO, position, p.topk);
-            start = tile_start[t];
-            pieces = (start + n - 1) / quota - start / quota + 1;
-            tickets[t] = 0;
-        }
-        uint32_t total;
-        const uint32_t offset = block_exclusive_scan(pieces, scratch, total);
-        if (t < live_tokens) {
-            const uint32_t c0 = start / quota;
-            for (uint32_t j = 0; j < pieces; ++j) {
-                const uint32_t c = c0 + j;
-                const uint32_t lo_flat = max(start, c * quota), hi_flat = min(start + n, (c + 1) * quota);
-                const uint32_t index = item_carry + offset + j;
-                uint4 *dst = reinterpret_cast<uint4 *>(items + index);
+    uint32_t my_pieces = 0, start = tile_base;
+    for (uint32_t t = t_begin; t < t_end; ++t) {
+        uint32_t batch; int32_t position;
+        const uint32_t n = tiles_of(t, batch, position);
+        my_pieces += (start + n - 1) / quota - start / quota + 1;
+        start += n;
+    }
+    uint32_t item_carry;                       // items in all
+    uint32_t index = block_exclusive_scan(my_pieces, sc->scan, item_carry);
+    start = tile_base;
+    // this CTA's flat tile range is [me * quota, (me + 1) * quota): skip the scan of tokens outside it
+    if (start < (me + 1) * quota && start + my_tiles > me * quota) {
+        for (uint32_t t = t_begin; t < t_end; ++t) {
+            uint32_t batch; int32_t position;
+            const uint32_t n = tiles_of(t, batch, position);
+            const uint32_t c0 = start / quota, pieces = (start + n - 1) / quota - c0 + 1;
+            if (me >= c0 && me < c0 + pieces) {
+                const uint32_t j = me - c0;
+                const uint32_t lo_flat = max(start, me * quota), hi_flat = min(start + n, (me + 1) * quota);
+                uint4 *dst = reinterpret_cast<uint4 *>(items + index + j);
                 dst[0] = make_uint4(t, batch, (uint32_t)position, lo_flat - start);
                 dst[1] = make_uint4(hi_flat - start, j, pieces, c0);
-                if (lo_flat == c * quota) cta_first[c] = index;
+                atomicMin(&sc->first, index + j);
+                atomicAdd(&sc->count, 1u);
             }
+            index += pieces;
+            start += n;
         }
-        item_carry += total;
     }
     __syncthreads();
-    for (uint32_t c = tid; c <= grid; c += kPlanThreads)
-        if (cta_first[c] == 0xffffffffu) cta_first[c] = item_carry;
-    if (tid == 0) {
+    PlanResult r;
+    r.first = sc->count ? sc->first : 0u;
+    r.end = r.first + sc->count;
+    r.live_tokens = live_tokens;
+    if (me == 0 && tid == 0) {
+        PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
         header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
-        header->quota = quota; header->n_items = item_carry; header->status = kStatusOk; header->grid = grid;
-        header->pad = 0;
+        header->quota = quota; header->n_items = item_carry; header->grid = grid;
     }
+    __syncthreads();          // the scratch area is handed back to the KV ring
+    return r;
 }
-
 // ------------------------------------------------------------------ decode kernel pieces
 struct Shared {
     uint32_t base;              // shared-space address of the aligned region
@@ -1087,7 +1095,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t x)
 }
 
 template <int RATIO, bool DEBUG>
-__device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const PlanHeader *header,
+__device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const uint32_t live_tokens,
                                 const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
     const uint32_t ch = threadIdx.x - 256u;        // 0..127
@@ -1110,7 +1118,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 
     // rows past the live token count are cleared (csrc/kernels/c8/attention_impl.h:443-460 of the reference)
     {
-        const uint32_t live = header->live_tokens;
+        const uint32_t live = live_tokens;
         for (uint32_t t = live + blockIdx.x; t < p.tokens; t += gridDim.x) {
             uint4 *o = reinterpret_cast<uint4 *>(p.out) + (uint64_t)t * 512u;
             for (uint32_t i = ch; i < 512u; i += 128u) o[i] = make_uint4(0, 0, 0, 0);
@@ -1298,10 +1306,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
 #endif
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
-    const PlanHeader *header = reinterpret_cast<const PlanHeader *>(ws);
-    const uint32_t *cta_first = reinterpret_cast<const uint32_t *>(ws + kWsCtaFirst);
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
-    const uint32_t first = cta_first[blockIdx.x], end = cta_first[blockIdx.x + 1];
+    const PlanResult plan = plan_cta<RATIO>(p, gridDim.x, reinterpret_cast<PlanScratch *>(sm.ptr + kSmKv));
+    const uint32_t first = plan.first, end = plan.end;
 
     // Roles by warpgroup (four warps, one per SM sub-partition); the register file is re-divided
     // first: the groups that need few registers release them before the others grow.
@@ -1310,7 +1317,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, first, end, tmem);
     } else if (warp < kWarpProducer) {
         registers_acquire<kRegsAccumulate>();
-        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, header, items, first, end, tmem);
+        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, plan.live_tokens, items, first, end, tmem);
     } else if (warp < kWarpMma || warp >= kWarpProducerB) {
         registers_release<kRegsProducer>();
         if (TMA && lane == 0) {
@@ -1329,7 +1336,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
             // the whole warp runs the issue loop and one elected lane issues: with converged control
             // flow the operand descriptors live in uniform registers, which halves the cost per MMA
             if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
-            else mma_pv_loop(sm, cta_first, items, first, end, tmem);
+            else mma_pv_loop(sm, nullptr, items, first, end, tmem);
             __syncwarp();
         }
     }
@@ -1430,8 +1437,9 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
     if (tma) tma = make_row_map(&ori_map, a.ori) && make_row_map(&cmp_map, a.cmp) &&
                    (RATIO != 128 || make_page_map(&cmp_page_map, a.cmp, a.cmpStride));
     if (!tma) { memset(&ori_map, 0, sizeof(ori_map)); memset(&cmp_map, 0, sizeof(cmp_map)); }
-    plan_kernel<RATIO><<<1, kPlanThreads, 0, stream>>>(a, grid);
-    e = cudaGetLastError();
+    // The split-K tickets and the status word start every launch at zero; everything else in the
+    // workspace is written by the kernel before it is read.
+    e = cudaMemsetAsync(reinterpret_cast<void *>(a.workspace), 0, ws_partials(a.tokens), stream);
     if (e != cudaSuccess) return (int)e;
     SharedKVDebug d = {};
     if (debug) {

@@ -16,7 +16,7 @@ operators with host buffers: per step and layer the new KV row of every request,
 (C4) the top-k selections are copied from pinned host memory, the cache writer and the
 attention run, and the BF16 output is copied back (three streams, so copies overlap compute).
 `roofline` is for the layer kind with the larger share of the step (`roofline_other` for the
-other): algorithmic KV bytes per launch over its mean CUDA-event duration, plan kernel included.
+other): algorithmic KV bytes per launch over its mean CUDA-event duration (the call's memset included).
 `--workload writer` times the paged cache writer instead (65 536 rows into the original cache and
 16 384 into the ratio-4 compressed cache per step) and prints rows/s.
 `--impl reference` times the CPU restatement of the reference's Python path (the reference
@@ -557,7 +557,7 @@ def main():
                    "kv_resident_gb_rank0": work.kv_bytes_resident / 1e9, "l2": "inputs larger than L2 (KV touched per step >> 126 MB)"
                    if args.workload != "c128" else f"rotating {layers} cache copies, each launch reads a region not touched for {layers - 1} launches"},
         "per_gpu_value": value / world, "kv_gbs": kv_gbs, "kv_gbs_per_gpu": kv_gbs / world,
-        "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}> (+ its plan kernel)"),
+        "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}> (+ the memset in front of it)"),
         "roofline_other": {f"decode_kernel<{r}>": v for r, v in roof.items() if r != dominant},
         "cpu_baseline": None if not cpu_n else {
             "value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": "port",

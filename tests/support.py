@@ -59,7 +59,7 @@ def synthetic_scale(rows):
 
 def device_tile_parts(case, ctas):
     """Which piece each 128-key tile of each token belongs to when the flat tile list of a
-    launch is cut into `ctas` equal contiguous ranges (the CUDA plan kernel's rule): a C4
+    launch is cut into `ctas` equal contiguous ranges (the CUDA kernel's work-split rule): a C4
     token with at least one compressed row has 1 + ceil(topk / 128) tiles, a C128 token
     1 + ceil(rows / 128), a token that sees no compressed row has 1."""
     counts = []
