@@ -210,13 +210,14 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
 
     if (tid == 0) { sc->live = 0; sc->mismatch = 0xffffffffu; sc->first = 0xffffffffu; sc->count = 0; }
     const bool staged = p.batch + 1u <= kPlanStaged;
+    const int32_t seq_first = tid < p.batch ? seq[tid] : 0;      // in flight together with the cuQ reads
     if (staged)
         for (uint32_t b = tid; b <= p.batch; b += kThreads) sc->cu[b] = cu_global[b];
     __syncthreads();
     const int32_t *cu = staged ? sc->cu : cu_global;
     uint32_t live = 0, mismatch = 0xffffffffu;
     for (uint32_t b = tid; b < p.batch; b += kThreads) {
-        if (seq[b] > 0 && cu[b + 1] >= 0) live = b + 1;
+        if ((b == tid ? seq_first : seq[b]) > 0 && cu[b + 1] >= 0) live = b + 1;
         if (cu[b + 1] != (int32_t)(b + 1) && mismatch == 0xffffffffu) mismatch = b;
     }
     if (live) atomicMax(&sc->live, live);

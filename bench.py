@@ -385,6 +385,7 @@ def main():
     parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="launch every layer from the host instead of replaying a captured step")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -423,24 +424,47 @@ def main():
         else:
             ops[index % layers].run()
 
-    # ---- resident-in-HBM timing, with per-layer events for the roofline
+    # ---- resident-in-HBM timing: K replays of a CUDA graph that holds one step (the serving stack
+    # of the reference replays captured decode steps too), then the same K steps launched one by
+    # one with events around every layer for the per-kernel roofline figures
     for i in range(args.warmup):
         step(i)
+    torch.cuda.synchronize()
+    graphs = None
+    if not args.no_graph:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        graphs = []
+        with torch.cuda.stream(side):
+            for i in range(1 if sequence is not None else layers):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step(i)
+                graphs.append(g)
+        torch.cuda.current_stream(device).wait_stream(side)
+        for i in range(args.warmup):
+            graphs[i % len(graphs)].replay()
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
-    marks = []
     begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     begin.record()
+    for i in range(args.steps):
+        if graphs is not None:
+            graphs[i % len(graphs)].replay()
+        else:
+            step(i)
+    finish.record()
+    barrier()
+    elapsed_ms = begin.elapsed_time(finish)
+    marks = []
     for i in range(args.steps):
         which = sequence if sequence is not None else [i % layers]
         for layer in which:
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(); ops[layer].run(); b.record()
             marks.append((layer, a, b))
-    finish.record()
     barrier()
     clocks = sampler.stop() if sampler else None
-    elapsed_ms = begin.elapsed_time(finish)
     per_kind = {}
     for layer, a, b in marks:
         ratio = work.layers[layer].ratio
@@ -554,7 +578,8 @@ def main():
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": label, "requests": args.requests if args.workload == "box" else work.requests,
                    "requests_on_rank0": work.requests, "layers_per_gpu": layers, "queries_per_step_rank0": queries_per_step,
-                   "kv_resident_gb_rank0": work.kv_bytes_resident / 1e9, "l2": "inputs larger than L2 (KV touched per step >> 126 MB)"
+                   "kv_resident_gb_rank0": work.kv_bytes_resident / 1e9,
+                   "launch": "host launches" if args.no_graph else "CUDA graph replay of one step", "l2": "inputs larger than L2 (KV touched per step >> 126 MB)"
                    if args.workload != "c128" else f"rotating {layers} cache copies, each launch reads a region not touched for {layers - 1} launches"},
         "per_gpu_value": value / world, "kv_gbs": kv_gbs, "kv_gbs_per_gpu": kv_gbs / world,
         "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}> (+ the memset in front of it)"),
@@ -563,7 +588,7 @@ def main():
             "value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": "port",
             "sample": f"{cpu_n} queries, batches of 8 requests per layer kind drawn from rank 0's requests",
             "kv_gbs": cpu_rows * ROW_BYTES / 1e9},
-        "e2e": e2e, "gpu_launches": 2 * len(marks), "clocks": clocks,
+        "e2e": e2e, "gpu_launches": len(marks), "clocks": clocks,
     }
     print(json.dumps(line))
     if world > 1:
