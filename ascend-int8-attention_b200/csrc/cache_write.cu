@@ -23,7 +23,12 @@ namespace sharedkv {
 namespace {
 
 constexpr int kWriterThreads = 256;          // 8 warps
-constexpr int kRowsInFlight = 4;             // rows a warp keeps in flight per iteration
+#ifndef SHAREDKV_WRITER_ROWS
+#define SHAREDKV_WRITER_ROWS 3
+#define SHAREDKV_WRITER_CTAS 4
+#endif
+constexpr int kRowsInFlight = SHAREDKV_WRITER_ROWS;       // rows a warp keeps in flight per iteration
+constexpr int kWriterCtasPerSm = SHAREDKV_WRITER_CTAS;    // resident CTAs per SM the vector kernel is compiled for
 
 __device__ __forceinline__ uint32_t quantize4(uint32_t lo2, uint32_t hi2, const float *inv)
 {
@@ -48,6 +53,9 @@ __device__ __forceinline__ bool resolve_slot(const CacheWriteArgs &p, uint32_t r
     if (Paired) {
         page = first;
         offset = (long long)slots[(uint64_t)row * p.slotStride + p.slotColumnStride];
+    } else if ((p.pageSize & (p.pageSize - 1u)) == 0u) {        // power-of-two pages (32 rows in serving): no division
+        page = first >> (31 - __clz((int)p.pageSize));
+        offset = first & (long long)(p.pageSize - 1u);
     } else {
         page = first / (long long)p.pageSize;
         offset = first % (long long)p.pageSize;
@@ -59,7 +67,7 @@ __device__ __forceinline__ bool resolve_slot(const CacheWriteArgs &p, uint32_t r
 
 // Vector path: update rows and cache rows are 16-byte aligned.
 template <class Index, bool Paired>
-__global__ void __launch_bounds__(kWriterThreads) cache_write_vec(const CacheWriteArgs p)
+__global__ void __launch_bounds__(kWriterThreads, kWriterCtasPerSm) cache_write_vec(const CacheWriteArgs p)
 {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kWriterThreads + threadIdx.x) >> 5;
@@ -136,7 +144,8 @@ cudaError_t launch_variant(const CacheWriteArgs &a, bool vec, cudaStream_t strea
     } else {
         blocks = (a.tokens + warps_per_block - 1) / warps_per_block;
     }
-    const uint32_t cap = (uint32_t)sms * 8u;      // 8 resident 256-thread CTAs per SM
+    // one wave: no more CTAs than are resident at once, each looping over its share of the rows
+    const uint32_t cap = (uint32_t)sms * (vec ? (uint32_t)kWriterCtasPerSm : 8u);
     if (blocks > cap) blocks = cap;
     if (blocks == 0) return cudaSuccess;
     if (vec) cache_write_vec<Index, Paired><<<blocks, kWriterThreads, 0, stream>>>(a);

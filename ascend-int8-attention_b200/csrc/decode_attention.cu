@@ -877,6 +877,11 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
         const uint32_t uses_before = kind == 0 ? k : k >> 1;
         char *qdst = sm.ptr + kSmQ + qbuf * 8192u;
         const uint4 *src = reinterpret_cast<const uint4 *>(p.q + (uint64_t)it.token * 8192u) + lane * 2u;
+        if (cur.item + 1 < cur.items_end) {        // the next item's query rows start their way to L2 now
+            const char *next = reinterpret_cast<const char *>(p.q) + (uint64_t)cur.next_lo.x * 8192u + lane * 256u;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(next));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(next + 128));
+        }
         uint4 raw[4][2];                           // four heads at a time keeps the warp inside its register budget
         if (used) {
 #pragma unroll
@@ -911,16 +916,21 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
                     uint32_t hi[4], lo[4];
 #pragma unroll
                     for (int w = 0; w < 4; ++w) {
-                        int ch[4], cl[4];
+                        // Round-half-even through the adder: x + 1.5 * 2^23 leaves the rounded integer in
+                        // the low mantissa bits (two's complement in the low byte for |x| <= 128).  The
+                        // clamp to +-127 of the reference is an identity here: |f| <= amax, so |f / alpha|
+                        // exceeds 127 by rounding error only, which rounds to +-127 with residual 0.
+                        uint32_t ch[4], cl[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float nrm = fminf(fmaxf(__fmul_rn(f[4 * w + e], rcp), -127.f), 127.f);
-                            const float hf = rintf(nrm);
-                            ch[e] = (int)hf;
-                            cl[e] = (int)rintf(__fmul_rn(__fsub_rn(nrm, hf), 127.f));
+                            const float nrm = __fmul_rn(f[4 * w + e], rcp);
+                            const float shifted = __fadd_rn(nrm, 12582912.f);
+                            const float hf = __fsub_rn(shifted, 12582912.f);
+                            ch[e] = __float_as_uint(shifted);
+                            cl[e] = __float_as_uint(__fadd_rn(__fmul_rn(__fsub_rn(nrm, hf), 127.f), 12582912.f));
                         }
-                        hi[w] = pack4(ch[0], ch[1], ch[2], ch[3]);
-                        lo[w] = pack4(cl[0], cl[1], cl[2], cl[3]);
+                        hi[w] = __byte_perm(__byte_perm(ch[0], ch[1], 0x0040), __byte_perm(ch[2], ch[3], 0x0040), 0x5410);
+                        lo[w] = __byte_perm(__byte_perm(cl[0], cl[1], 0x0040), __byte_perm(cl[2], cl[3], 0x0040), 0x5410);
                     }
                     const uint4 vh = make_uint4(hi[0], hi[1], hi[2], hi[3]), vl = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     *reinterpret_cast<uint4 *>(qdst + tile_offset(h, lane, 2048u)) = vh;
