@@ -43,7 +43,7 @@ METRIC = "decode attn queries/s/GPU & achieved HBM GB/s (INT8 KV) at 1/2/4/8 B20
 ROW_BYTES = 512
 # DRAM traffic (read + written) per algorithmic KV byte, from ncu captures of smaller launches of the
 # same kernels (profiles/decode_kernel_*.md); traffic grows in proportion to the queries processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.076, 128: 1.036}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.076, 128: 1.040}
 
 
 def measured_peaks():
