@@ -53,7 +53,7 @@ def save_case(name, case, oq, cq, ref, extra=None):
 
 
 def windowed_case(ref, *, ratio, queries, lengths, seed, topk=1024, edit_indices=None):
-    """Synthetic case of the BASELINE config family: lognormal per-channel spread, scale =
+    """Synthetic case of the benchmark configuration family: lognormal per-channel spread, scale =
     1.1 * absmax / 127, page tables that are random permutations of the page pool, and only
     the window pages of the original cache allocated (as a sliding-window allocator does)."""
     g = torch.Generator().manual_seed(seed)
@@ -100,7 +100,7 @@ def windowed_case(ref, *, ratio, queries, lengths, seed, topk=1024, edit_indices
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument('--reference', type=Path, default=Path('/root/reference'))
+    parser.add_argument('--reference', type=Path, required=True, help='checkout of the reference project')
     args = parser.parse_args()
     sys.path.insert(0, str(args.reference))
     from npu_sparse_attn_sharedkv_int8 import reference as ref
@@ -139,7 +139,7 @@ def main():
         oq, cq = ref.CacheQuantization.calibrate([case.ori]), ref.CacheQuantization.calibrate([case.cmp])
         save_case(f'unit_c{ratio}', replace(case, ori=oq.quantize(case.ori), cmp=cq.quantize(case.cmp)), oq, cq, ref)
 
-    # ---- BASELINE config 0: C4, B=2, T=1, contexts 4096 / 8192, top-k 1024, seed 0
+    # ---- benchmark configuration 0: C4, B=2, T=1, contexts 4096 / 8192, top-k 1024, seed 0
     case, oq, cq = windowed_case(ref, ratio=4, queries=[1, 1], lengths=[4096, 8192], seed=0)
     save_case('config0_c4', case, oq, cq, ref)
 
