@@ -546,7 +546,12 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 // Row fetch: one TMA gather of four consecutive slots x one 128-channel segment per lane
 // (lane = 4 * group + segment); for the compressed rows of a C128 layer, which fill whole pages,
 // four 4 KB page-segment boxes per warp; 16-byte cp.async copies when the page strides rule TMA out.
-constexpr int kLookahead = 2;          // two tiles (several microseconds) cover the latency of either read
+#ifndef SHAREDKV_LOOKAHEAD
+#define SHAREDKV_LOOKAHEAD 1
+#endif
+// One tile of the set (= two tiles of the CTA, about 4 us) covers the latency of either read; a
+// deeper pipeline only lengthens the start of the kernel (measured: 2 is 3 % slower than 1).
+constexpr int kLookahead = SHAREDKV_LOOKAHEAD;
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
 template <int RATIO, bool TMA>
