@@ -124,3 +124,21 @@ def test_serving_batch_against_the_oracle_and_its_invariants(serving_batch, laye
     # every output row is a convex combination of dequantised rows plus the sink's share: finite, bounded
     bound = float((127 * torch.maximum(layer.ori_scale, layer.cmp_scale)).max())
     assert torch.isfinite(out.float()).all() and float(out.float().abs().max()) <= bound * 1.01
+
+
+@pytest.mark.parametrize("ratio", (4, 128))
+def test_many_query_tokens_per_request(ratio):
+    """Chunked-prefill shapes run through the decode kernel as they are: every token is an
+    independent query with its own causal position (the reference serves up to 16 384 tokens per
+    request on this core, tests/npu/test_capacity.py:41-51).  A 300-token and a 17-token chunk."""
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    source = make_case(query_lengths=(300, 17), seq_lens=(2500, 4300), heads=8, ratio=ratio, topk=1024, seed=5)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    op = prepared(case.to(DEVICE), oq.scale, cq.scale, return_lse=True)
+    out = op.run()
+    torch.cuda.synchronize()
+    expected, expected_lse = oracle.attention_tiled(case, oq.scale, cq.scale, return_lse=True)
+    m = error_metrics(out.cpu().float(), expected.float())
+    assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+    torch.testing.assert_close(op.lse.cpu(), expected_lse, rtol=1e-4, atol=1e-4)
