@@ -11,6 +11,7 @@
   exactly, so codes and logits do not change).
 """
 from dataclasses import replace
+from types import SimpleNamespace
 
 import pytest
 import torch
@@ -142,3 +143,39 @@ def test_many_query_tokens_per_request(ratio):
     m = error_metrics(out.cpu().float(), expected.float())
     assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
     torch.testing.assert_close(op.lse.cpu(), expected_lse, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("ratio", (4, 128))
+def test_twelve_thousand_requests_in_one_launch(ratio):
+    """More requests than the work split keeps in shared memory (it then reads cuQ from global
+    memory), sixteen tokens per planning thread, thousands of one- and two-tile items per CTA."""
+    from npu_sparse_attn_sharedkv_int8.reference import SharedKVCase
+    batch, pages = 12000, 512
+    g = torch.Generator().manual_seed(77)
+    lengths = torch.randint(1, 400, (batch,), generator=g, dtype=torch.int32)
+    # requests share a small pool of pages (reads may alias), so the case stays small on the host
+    case = SharedKVCase(
+        q=torch.randn(batch, 8, 512, generator=g).bfloat16(),
+        ori=torch.randint(-127, 128, (pages, 32, 1, 512), generator=g, dtype=torch.int8),
+        ori_block_table=torch.randint(0, pages, (batch, 13), generator=g, dtype=torch.int32),
+        cu_q=torch.arange(batch + 1, dtype=torch.int32), seq_lens=lengths, sink=torch.linspace(-2, 2, 8),
+        cmp=torch.randint(-127, 128, (pages, 32, 1, 512), generator=g, dtype=torch.int8),
+        cmp_block_table=torch.randint(0, pages, (batch, 4), generator=g, dtype=torch.int32),
+        cmp_indices=torch.randint(-1, 110, (batch, 1, 1024), generator=g, dtype=torch.int32) if ratio == 4 else None,
+        ratio=ratio)
+    scale = SimpleNamespace(scale=torch.rand(512, generator=g) * 0.02 + 0.005)
+    oq = cq = scale
+    op = prepared(case.to(DEVICE), oq.scale, cq.scale, return_lse=True)
+    out = op.run().cpu()
+    torch.cuda.synchronize()
+    lse = op.lse.cpu()
+    for first in (0, 5000, batch - 40):                 # three slices of forty requests against the oracle
+        rows = slice(first, first + 40)
+        part = replace(case, q=case.q[rows], ori_block_table=case.ori_block_table[rows], cmp_block_table=case.cmp_block_table[rows],
+                       cu_q=torch.arange(41, dtype=torch.int32), seq_lens=case.seq_lens[rows],
+                       cmp_indices=case.cmp_indices[rows] if case.cmp_indices is not None else None)
+        expected, expected_lse = oracle.attention_tiled(part, oq.scale, cq.scale, return_lse=True)
+        m = error_metrics(out[rows].float(), expected.float())
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, (first, m)
+        torch.testing.assert_close(lse[rows], expected_lse, rtol=1e-4, atol=1e-4)
+    assert torch.isfinite(out.float()).all()
