@@ -189,8 +189,7 @@ __device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_ba
 // part).  The live shape comes from cuQ / seqLens on the device, so a captured graph follows the
 // live batch.  Every live token has 1 + ceil(compressed rows / 128) tiles; the flat tile list is cut
 // into `grid` equal ranges; the pieces of tokens that fall into this CTA's range become its items,
-// written to the workspace at the positions they have in the global item order (so that two CTAs
-// never write the same entry).  `scratch` is shared memory the roles do not use yet (the KV ring).
+// written to workspace entries no other CTA uses (entry = token + CTA number).  `scratch` is shared memory the roles do not use yet (the KV ring).
 struct PlanResult {
     uint32_t first, end, live_tokens;
 };
@@ -229,8 +228,8 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     // one query token per request (plain decode): token t belongs to request t
     const bool one_each = live_tokens == live_batch && cu[0] == 0 && sc->mismatch >= live_batch;
 
-    // Thread i owns the consecutive tokens [i * per, (i + 1) * per): two block-wide scans in all,
-    // one of tiles (gives the quota per CTA) and one of pieces (gives the positions of the items).
+    // Thread i owns the consecutive tokens [i * per, (i + 1) * per); one block-wide scan of their tile
+    // counts gives every thread its flat tile offset and the CTA the total (hence the quota).
     const uint32_t per = (live_tokens + kThreads - 1) / kThreads;
     const uint32_t t_begin = min(tid * per, live_tokens), t_end = min(t_begin + per, live_tokens);
     auto tiles_of = [&](uint32_t t, uint32_t &batch, int32_t &position) {
@@ -248,35 +247,28 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     const uint32_t quota = total_tiles ? (total_tiles + grid - 1) / grid : 1;
     const uint32_t me = blockIdx.x;
 
-    uint32_t my_pieces = 0, start = tile_base;
-    for (uint32_t t = t_begin; t < t_end; ++t) {
-        uint32_t batch; int32_t position;
-        const uint32_t n = tiles_of(t, batch, position);
-        my_pieces += (start + n - 1) / quota - start / quota + 1;
-        start += n;
-    }
-    uint32_t item_carry;                       // items in all
-    uint32_t index = block_exclusive_scan(my_pieces, sc->scan, item_carry);
-    start = tile_base;
-    // this CTA's flat tile range is [me * quota, (me + 1) * quota): skip the scan of tokens outside it
+    // This CTA's flat tile range is [me * quota, (me + 1) * quota).  The tokens that overlap it are
+    // consecutive, so an item needs no second scan for its place: the piece of token t that belongs
+    // to CTA c is stored at index t + c, which is unique and increasing along (token, piece) because
+    // a token's pieces sit in consecutive CTAs and the next token starts in the last of them or later.
+    uint32_t start = tile_base;
     if (start < (me + 1) * quota && start + my_tiles > me * quota) {
         for (uint32_t t = t_begin; t < t_end; ++t) {
             uint32_t batch; int32_t position;
             const uint32_t n = tiles_of(t, batch, position);
             const uint32_t c0 = start / quota, pieces = (start + n - 1) / quota - c0 + 1;
             if (me >= c0 && me < c0 + pieces) {
-                const uint32_t j = me - c0;
                 const uint32_t lo_flat = max(start, me * quota), hi_flat = min(start + n, (me + 1) * quota);
-                uint4 *dst = reinterpret_cast<uint4 *>(items + index + j);
+                uint4 *dst = reinterpret_cast<uint4 *>(items + t + me);
                 dst[0] = make_uint4(t, batch, (uint32_t)position, lo_flat - start);
-                dst[1] = make_uint4(hi_flat - start, j, pieces, c0);
-                atomicMin(&sc->first, index + j);
+                dst[1] = make_uint4(hi_flat - start, me - c0, pieces, c0);
+                atomicMin(&sc->first, t + me);
                 atomicAdd(&sc->count, 1u);
             }
-            index += pieces;
             start += n;
         }
     }
+    const uint32_t item_carry = live_tokens;      // header only: tokens, not counting the extra pieces
     __syncthreads();
     PlanResult r;
     r.first = sc->count ? sc->first : 0u;
