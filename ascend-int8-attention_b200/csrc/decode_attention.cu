@@ -10,8 +10,8 @@
 //                  code csrc/kernels/c8/attention_impl.h:121-137), counts the 128-key tiles of
 //                  every query token, cuts the flat tile list into one contiguous range per CTA
 //                  and writes its own work items into the workspace (plan_cta).
-//     warps 12-15, 20-23  producers (even / odd tiles): row selection -> page table -> row id, two
-//                  tiles ahead; rows land in a 3-stage ring of 128-key x 512-byte tiles (128-byte
+//     warps 12-15, 20-23  producers (even / odd tiles): row selection -> page table -> row id, each a
+//                  tile ahead of the next; rows land in a 3-stage ring of 128-key x 512-byte tiles (128-byte
 //                  swizzle) by TMA row gathers (whole-page boxes for C128 compressed rows, 16-byte
 //                  cp.async when the page strides rule TMA out)
 //     warps 18-19  query encode: fold scale, absmax, hi / lo INT8 planes of the next item
@@ -171,7 +171,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
     return result;
 }
 
-// ------------------------------------------------------------------ plan kernel
+// ------------------------------------------------------------------ work split
 constexpr uint32_t kPlanStaged = 11776;      // cuQ entries kept in shared memory (46 KB)
 
 // Request that owns query token t: the b with cu[b] <= t < cu[b + 1], 0 <= b < live_batch.
