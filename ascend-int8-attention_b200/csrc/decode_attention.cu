@@ -172,6 +172,10 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
 }
 
 // ------------------------------------------------------------------ work split
+#ifndef SHAREDKV_ITEM_COST
+#define SHAREDKV_ITEM_COST 1
+#endif
+constexpr uint32_t kItemCost = SHAREDKV_ITEM_COST;      // cost of a token's once-only work, in tiles
 constexpr uint32_t kPlanStaged = 11776;      // cuQ entries kept in shared memory (46 KB)
 
 // Request that owns query token t: the b with cu[b] <= t < cu[b + 1], 0 <= b < live_batch.
@@ -244,18 +248,23 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     }
     uint32_t total_tiles;
     const uint32_t tile_base = block_exclusive_scan(my_tiles, sc->scan, total_tiles);
-    const uint32_t quota = total_tiles ? (total_tiles + grid - 1) / grid : 1;
+    // The ranges are cut in units of cost, not of tiles: a token costs its tiles plus kItemCost units
+    // for what happens once per token (query encode, final normalisation and store), placed in front
+    // of its first tile.  Tile j of token t sits at cost position (tiles before t) + kItemCost (t + 1) + j.
+    const uint32_t total_cost = total_tiles + kItemCost * live_tokens;
+    const uint32_t quota = total_cost ? (total_cost + grid - 1) / grid : 1;
     const uint32_t me = blockIdx.x;
 
     // This CTA's flat tile range is [me * quota, (me + 1) * quota).  The tokens that overlap it are
     // consecutive, so an item needs no second scan for its place: the piece of token t that belongs
     // to CTA c is stored at index t + c, which is unique and increasing along (token, piece) because
     // a token's pieces sit in consecutive CTAs and the next token starts in the last of them or later.
-    uint32_t start = tile_base;
-    if (start < (me + 1) * quota && start + my_tiles > me * quota) {
+    uint32_t start = tile_base + kItemCost * t_begin;
+    if (start < (me + 1) * quota && start + my_tiles + kItemCost * (t_end - t_begin) > me * quota) {
         for (uint32_t t = t_begin; t < t_end; ++t) {
             uint32_t batch; int32_t position;
             const uint32_t n = tiles_of(t, batch, position);
+            start += kItemCost;
             const uint32_t c0 = start / quota, pieces = (start + n - 1) / quota - c0 + 1;
             if (me >= c0 && me < c0 + pieces) {
                 const uint32_t lo_flat = max(start, me * quota), hi_flat = min(start + n, (me + 1) * quota);

@@ -57,9 +57,12 @@ def synthetic_scale(rows):
     return CacheQuantization((rows.float().reshape(-1, 512).abs().amax(0) * 1.1 / 127).clamp_min(1e-8))
 
 
+ITEM_COST = 1                 # the kernel's kItemCost
+
+
 def device_tile_parts(case, ctas):
     """Which piece each 128-key tile of each token belongs to when the flat tile list of a
-    launch is cut into `ctas` equal contiguous ranges (the CUDA kernel's work-split rule): a C4
+    launch is cut into `ctas` contiguous ranges of equal cost (the CUDA kernel's work-split rule): a C4
     token with at least one compressed row has 1 + ceil(topk / 128) tiles, a C128 token
     1 + ceil(rows / 128), a token that sees no compressed row has 1."""
     counts = []
@@ -72,10 +75,12 @@ def device_tile_parts(case, ctas):
                 counts.append(1 + (-(-case.cmp_indices.shape[-1] // 128) if rows else 0))
             else:
                 counts.append(1 + -(-rows // 128))
-    total = sum(counts)
+    # ranges are cut in units of cost: a token's tiles plus ITEM_COST units in front of its first tile
+    total = sum(counts) + ITEM_COST * len(counts)
     quota = max(1, -(-total // ctas))
     parts, start = {}, 0
     for token, n in enumerate(counts):
+        start += ITEM_COST
         parts[token] = [(start + j) // quota - start // quota for j in range(n)]
         start += n
     return parts
