@@ -127,6 +127,45 @@ def build_workload(args, rank, world):
     return work, workload_label(args)
 
 
+# --------------------------------------------------------------------------- host memory placement
+class HostMemoryNear:
+    """While active, this process runs on the CPU cores next to CUDA device `index` (as NVML reports
+    them), so that pinned host buffers allocated inside land in that GPU's NUMA node; with several
+    ranks on one host, copies through the other socket cost bandwidth.  Does nothing when NVML or
+    the affinity calls are unavailable.  The process's CPU affinity is restored on exit; no GPU
+    setting is touched."""
+
+    def __init__(self, index):
+        self.index, self.saved = index, None
+
+    def __enter__(self):
+        try:
+            if self.index < 0:
+                return self
+            import pynvml
+            props = torch.cuda.get_device_properties(self.index)
+            bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+            cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+            allowed = os.sched_getaffinity(0)
+            if cpus & allowed:
+                self.saved = allowed
+                os.sched_setaffinity(0, cpus & allowed)
+        except Exception:
+            self.saved = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.saved is not None:
+            try:
+                os.sched_setaffinity(0, self.saved)
+            except Exception:
+                pass
+        return False
+
+
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -404,6 +443,8 @@ def main():
     parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--e2e-graph", action="store_true", help="replay a captured step in the host-buffer measurement too")
+    parser.add_argument("--no-host-affinity", action="store_true", help="allocate host buffers without moving next to the GPU")
     parser.add_argument("--no-graph", action="store_true", help="launch every layer from the host instead of replaying a captured step")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -498,9 +539,12 @@ def main():
     e2e = None
     if not args.no_e2e:
         tokens = work.tokens
-        host_q = [torch.randn(tokens, 8, 512).bfloat16().pin_memory() for _ in range(min(layers, 4))]
-        host_rows = torch.randn(tokens, 512).bfloat16().pin_memory()
-        host_out = [torch.empty(tokens, 8, 512, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        with HostMemoryNear(-1 if args.no_host_affinity else local):
+            host_q = [torch.randn(tokens, 8, 512).bfloat16().pin_memory() for _ in range(min(layers, 4))]
+            host_rows = torch.randn(tokens, 512).bfloat16().pin_memory()
+            host_out = [torch.empty(tokens, 8, 512, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+            host_idx_source = next((l.cmp_indices for l in work.layers if l.cmp_indices is not None), None)
+            host_idx_early = host_idx_source.cpu().pin_memory() if host_idx_source is not None else None
         host_idx = None
         # the new token of request b lands in the last row of its window: logical row seq_len - 1
         last = (work.seq_lens_host - 1)
@@ -513,13 +557,12 @@ def main():
             dev_rows.append(torch.empty(tokens, 512, dtype=torch.bfloat16, device=device))
             writers.append(PreparedCacheWrite(layer.ori, dev_rows[i], slots, inverse))
             if layer.cmp_indices is not None and host_idx is None:
-                host_idx = layer.cmp_indices.cpu().pin_memory()
+                host_idx = host_idx_early
         # Three streams: inputs of layer i + 1 cross PCIe while layer i computes and layer i - 1's
         # output goes back.  Every layer owns its device-side Q, rows, indices and output, so the only
         # ordering needed is copy-in -> compute -> copy-out per layer, and "the previous use of this
         # layer's buffers is over" before they are overwritten.
         copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
-        main_stream = torch.cuda.current_stream(device)
         staged = [torch.cuda.Event() for _ in range(layers)]
         computed = [torch.cuda.Event() for _ in range(layers)]
         returned = [torch.cuda.Event() for _ in range(layers)]
@@ -528,6 +571,7 @@ def main():
         def e2e_layer(i, slot):
             nonlocal h2d, d2h
             layer = work.layers[i]
+            main = torch.cuda.current_stream(device)
             with torch.cuda.stream(copy_in):
                 if used[i]:
                     copy_in.wait_event(computed[i])
@@ -538,12 +582,12 @@ def main():
                     layer.cmp_indices.copy_(host_idx, non_blocking=True)
                     moved += host_idx.numel() * 4
                 staged[i].record(copy_in)
-            main_stream.wait_event(staged[i])
+            main.wait_event(staged[i])
             if used[i]:
-                main_stream.wait_event(returned[i])       # the output of the previous step has been read
+                main.wait_event(returned[i])              # the output of the previous step has been read
             writers[i].run()
             out = ops[i].run()
-            computed[i].record(main_stream)
+            computed[i].record(main)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(computed[i])
                 host_out[slot].copy_(out, non_blocking=True)
@@ -553,27 +597,65 @@ def main():
             d2h += out.numel() * 2
 
         def e2e_step(index):
+            main = torch.cuda.current_stream(device)
+            if torch.cuda.is_current_stream_capturing():  # a captured step forks its copy streams from the capture stream;
+                copy_in.wait_stream(main)                 # launched from the host, the copies of step n + 1 may overlap
+                copy_out.wait_stream(main)                # the end of step n (buffers are guarded by the events below)
             which = sequence if sequence is not None else [index % layers]
             for n, i in enumerate(which):
                 e2e_layer(i, n & 1)
-            main_stream.wait_stream(copy_out)             # the step ends when its last result is on the host
+            main.wait_stream(copy_in)
+            main.wait_stream(copy_out)                    # the step ends when its last result is on the host
 
         for i in range(3):
             e2e_step(i)
+        torch.cuda.synchronize()
+        # Optionally one step (copies, writer and attention launches of every layer, on the three
+        # streams) is captured and replayed.  Off by default: replays do not overlap one step's last
+        # copies with the next step's first ones, which host launches do (measured 10 % slower at
+        # 1 and 2 GPUs); it pays only when the host cannot issue a step's launches fast enough.
+        e2e_graphs = None
+        if args.e2e_graph:
+            side = torch.cuda.Stream(device)
+            side.wait_stream(torch.cuda.current_stream(device))
+            e2e_graphs = []
+            with torch.cuda.stream(side):
+                for i in range(1 if sequence is not None else layers):
+                    used[:] = [False] * layers            # replays are ordered by the stream; no cross-step events
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        e2e_step(i)
+                    e2e_graphs.append(g)
+            torch.cuda.current_stream(device).wait_stream(side)
+            used[:] = [False] * layers
+            for i in range(2):
+                e2e_graphs[i % len(e2e_graphs)].replay()
+
+        def e2e_run(index):
+            if e2e_graphs is not None:
+                e2e_graphs[index % len(e2e_graphs)].replay()
+            else:
+                e2e_step(index)
+
         barrier()
         h2d = d2h = 0
+        used[:] = [False] * layers
+        e2e_step(0)                                       # one eager step only to count the bytes a step moves
+        torch.cuda.synchronize()
+        h2d_step, d2h_step = h2d, d2h
+        barrier()
         t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-        wall = time.perf_counter()
         t0.record()
         for i in range(args.steps):
-            e2e_step(i)
+            e2e_run(i)
         t1.record()
         barrier()
-        wall = time.perf_counter() - wall
+        h2d, d2h = h2d_step * args.steps, d2h_step * args.steps
         e2e_ms, _ = combine_ranks(max(t0.elapsed_time(t1), 0.0), [0], device, world)
         e2e = {"value": counts[0] / (e2e_ms / 1000), "unit": "queries/s",
                "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
-               "ms_per_step": e2e_ms / args.steps}
+               "ms_per_step": e2e_ms / args.steps,
+               "launch": "CUDA graph replay of one step (copies included)" if args.e2e_graph else "host launches on three streams"}
 
     if rank != 0:
         if world > 1:
