@@ -15,18 +15,19 @@ pytestmark = pytest.mark.gpu
 DEVICE = "cuda:0"
 
 
-def random_case(seed):
+def random_case(seed, force_topk=None, min_length=0):
     from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
     g = torch.Generator().manual_seed(1000 + seed)
     pick = lambda options: options[int(torch.randint(len(options), (1,), generator=g))]
-    ratio = pick((4, 128))
+    ratio = 4 if force_topk else pick((4, 128))
     batch = int(torch.randint(1, 7, (1,), generator=g))
     queries = [int(torch.randint(1, 5, (1,), generator=g)) for _ in range(batch)]
     top = pick((9000, 600, 40)) if ratio == 4 else pick((40000, 9000, 300))
     lengths = [max(q, int(math.exp(float(torch.rand(1, generator=g)) * math.log(top)))) for q in queries]
-    if seed % 5 == 0:
+    lengths = [max(v, min_length) for v in lengths]
+    if seed % 5 == 0 and not min_length:
         lengths[0] = queries[0]                                  # a request that consists of its query tokens only
-    topk = pick((1024, 1000, 256, 64)) if ratio == 4 else 1024
+    topk = force_topk or (pick((1024, 1000, 256, 64)) if ratio == 4 else 1024)
     source = make_case(query_lengths=tuple(queries), seq_lens=tuple(lengths), heads=8, ratio=ratio, topk=topk, seed=seed)
     oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
     case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
@@ -45,10 +46,11 @@ def random_case(seed):
     return case, oq.scale, cq.scale, stride, (16 if stride % 512 else 1024)
 
 
-@pytest.mark.parametrize("seed", range(24))
-def test_random_geometry(seed):
+@pytest.mark.parametrize("seed,topk", [(s, None) for s in range(24)] + [(30, 1000), (31, 64), (32, 130), (33, 1), (34, 1023), (35, -1000), (36, -200), (37, -129)])
+def test_random_geometry(seed, topk):
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
-    case, ori_scale, cmp_scale, stride, offset = random_case(seed)
+    # a negative width asks for contexts long enough that the selection is not packed (holes keep their slots)
+    case, ori_scale, cmp_scale, stride, offset = random_case(seed, abs(topk) if topk else None, 4200 if topk and topk < 0 else 0)
     dev = case.to(DEVICE)
     dev = replace(dev, ori=strided_pages(case.ori, DEVICE, stride, offset), cmp=strided_pages(case.cmp, DEVICE, stride, offset))
     op = PreparedAttention(dev, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), return_lse=True)
