@@ -121,7 +121,8 @@ struct Item {
     uint32_t tile_begin, tile_end, part, nparts, first_cta;
 };
 static_assert(sizeof(Item) == 32, "work item is two 16-byte loads");
-constexpr uint64_t kWsCtaFirst = 64;
+// bytes 0-63: PlanHeader; 64-1023 and the 4 x tokens bytes in front of the tickets are kept free (the
+// size formula is part of the ABI: sharedkv_workspace_bytes and its Python mirror)
 constexpr uint64_t kWsItems = 1024;
 __host__ __device__ inline uint64_t ws_tile_start(uint32_t tokens) { return kWsItems + 32ull * (tokens + kMaxCtas); }
 __host__ __device__ inline uint64_t ws_tickets(uint32_t tokens) { return ws_tile_start(tokens) + 4ull * tokens; }
@@ -1037,7 +1038,6 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (gt & 7u) * 16u;
             int p_hi[4], p_lo[4];
             float r[4];
-#pragma unroll
             const float4 q0 = reinterpret_cast<const float4 *>(slot_red)[0], q1 = reinterpret_cast<const float4 *>(slot_red)[1];
             const float4 q2 = reinterpret_cast<const float4 *>(slot_red)[2], q3 = reinterpret_cast<const float4 *>(slot_red)[3];
             const float tmaxes[4] = {fmaxf(fmaxf(q0.x, q1.x), fmaxf(q2.x, q3.x)), fmaxf(fmaxf(q0.y, q1.y), fmaxf(q2.y, q3.y)),
