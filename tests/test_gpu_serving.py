@@ -179,3 +179,25 @@ def test_twelve_thousand_requests_in_one_launch(ratio):
         assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, (first, m)
         torch.testing.assert_close(lse[rows], expected_lse, rtol=1e-4, atol=1e-4)
     assert torch.isfinite(out.float()).all()
+
+
+def test_two_streams_at_once():
+    """Two prepared operators with their own workspaces, launched back to back on two streams so
+    that their persistent kernels compete for the SMs: no CTA ever waits for another CTA, so the
+    launches interleave or serialise but both finish with the right answer."""
+    streams = [torch.cuda.Stream(device=DEVICE) for _ in range(2)]
+    jobs = []
+    for name, stream in zip(("config0_c4", "mixed_c128"), streams):
+        case, ori_scale, cmp_scale, z = load_case(name)
+        with torch.cuda.stream(stream):
+            op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
+        jobs.append((op, stream, bf16(z["out_s1"]).float()))
+    torch.cuda.synchronize()
+    for _ in range(20):
+        for op, stream, _ in jobs:
+            with torch.cuda.stream(stream):
+                op.run()
+    torch.cuda.synchronize()
+    for op, _, expected in jobs:
+        m = error_metrics(op.out.cpu().float(), expected)
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
