@@ -1,8 +1,9 @@
-"""C4 / C128 decode route: ABI guard, scratch sizing and the three launcher symbols.
+"""C4 / C128 decode route on CUDA: ABI guard, scratch sizing, launcher selection.
 
-Counterpart of the reference's default route (npu_sparse_attn_sharedkv_int8/c8_attention.py).
-Tiling, KV splitting and live-shape handling are decided on the device at every launch,
-so nothing here depends on sequence lengths.
+Counterpart of the reference's default route (npu_sparse_attn_sharedkv_int8/c8_attention.py:16-138)
+with the same module surface (`CORES HEADS DIM MAX_SPLITS WORKSPACE_BYTES enabled argument_type
+library supported prepare host_module native_host`).  Tiling, KV splitting and the live shape are
+decided on the device at every launch, so nothing here looks at sequence lengths.
 """
 import copy
 import ctypes
@@ -14,16 +15,18 @@ import torch
 
 from .runtime import _library, check, current_stream, native_launcher
 
-CORES = 148                 # persistent CTAs on a B200 (the reference: 24 AI cores); `blocks` is advisory
+CORES = 148                 # persistent CTAs on a B200 (24 AI cores in the reference); `blocks` is advisory
 HEADS = 8
 DIM = 512
 MAX_SPLITS = CORES          # a token's KV may be spread over at most one piece per CTA
-_MAX_CTAS = 160             # partial-result slots reserved by the library
+_MAX_CTAS = 160             # partial-result slots the library reserves
 _PARTIAL_FLOATS = HEADS * DIM + 16
+_VARIANTS = {"sparse": 20, "dense": 21, "sparse_small": 22}     # kernel ids of the host bridge
+_SMALL_C4_TOKENS = 24       # below this the reference selects its "small" C4 image (c4_small.cpp:21)
 
 
 def workspace_bytes(tokens):
-    """Scratch bytes one launch with `tokens` query rows needs (plan, tickets, partial sums).
+    """Scratch bytes one launch with `tokens` query rows needs (work items, tickets, partial sums).
     Python restatement of sharedkv_workspace_bytes(); a unit test keeps the two equal."""
     plan = 1024 + 32 * (tokens + _MAX_CTAS) + 4 * tokens + 4 * tokens
     return (plan + 255) // 256 * 256 + _MAX_CTAS * 2 * _PARTIAL_FLOATS * 4
@@ -34,10 +37,13 @@ WORKSPACE_BYTES = workspace_bytes(8192)
 
 
 def enabled():
-    value = os.environ.get('SHAREDKV_C8_DECODE', '1')
-    if value not in ('0', '1'):
-        raise ValueError('SHAREDKV_C8_DECODE must be 0 or 1')
-    return value == '1'
+    """SHAREDKV_C8_DECODE switch of the reference (c8_attention.py:33-37): unset or "1" is on."""
+    setting = os.environ.get("SHAREDKV_C8_DECODE", "1")
+    if setting == "1":
+        return True
+    if setting == "0":
+        return False
+    raise ValueError("SHAREDKV_C8_DECODE must be 0 or 1")
 
 
 def argument_type():
@@ -47,75 +53,72 @@ def argument_type():
 
 @lru_cache(maxsize=1)
 def library():
+    """The loaded CUDA library, after checking that it was built for this argument struct."""
     lib = _library()
     if lib.sharedkv_attention_args_size() != ctypes.sizeof(argument_type()):
-        raise RuntimeError('C8 host/device argument ABI mismatch')
+        raise RuntimeError("C8 host/device argument ABI mismatch")
     return lib
 
 
 def supported(entry):
-    """The geometry the CUDA kernels implement: eight heads, window 128, 32-row pages,
-    ratio 4 (top-k <= 1024, no explicit original slots) or ratio 128."""
-    if not getattr(entry, 'blocks', 0) or not hasattr(entry, 'args'):
+    """True for the geometry the CUDA kernels implement: eight heads, window 128, 32-row pages, no
+    explicit original slots, ratio 128 or ratio 4 with at most 1024 selections per token."""
+    args = getattr(entry, "args", None)
+    if not getattr(entry, "blocks", 0) or not isinstance(args, argument_type()):
         return False
-    p = entry.args
-    if not isinstance(p, argument_type()):
+    if args.tokens == 0 or args.batch == 0 or args.oriIndices:
         return False
-    return (
-        p.heads == HEADS
-        and p.tokens > 0
-        and p.batch > 0
-        and p.ratio in (4, 128)
-        and p.window == 128
-        and p.oriBlock == p.cmpBlock == 32
-        and not p.oriIndices
-        and (p.ratio != 4 or 0 < p.topk <= 1024)
-    )
+    if (args.heads, args.window, args.oriBlock, args.cmpBlock) != (HEADS, 128, 32, 32):
+        return False
+    return args.ratio == 128 or (args.ratio == 4 and 0 < args.topk <= 1024)
+
+
+def _launcher_name(args):
+    if args.ratio == 128:
+        return "dense"
+    return "sparse_small" if args.tokens < _SMALL_C4_TOKENS else "sparse"
 
 
 def prepare(entry, *, scratch_allocator=None, shared_storage=False):
-    """Bind scratch and the launcher to a validated entry; no device read-back.
+    """A copy of a validated entry bound to scratch and to its launcher; nothing is read back.
 
-    With shared_storage the caller has already placed a workspace of at least
-    workspace_bytes(tokens) in entry.workspace (tests use that to put guard bands around it).
+    Scratch comes from `scratch_allocator(name, shape, dtype, device)` (serving passes its
+    per-stream pool) or from torch.  With shared_storage the caller has already put a workspace of
+    at least workspace_bytes(tokens) in entry.workspace (tests surround it with guard bands).
+    Entries that are already prepared, or outside `supported`, are returned as they are.
     """
-    if getattr(entry, 'c8_dynamic', False) or not supported(entry):
+    if getattr(entry, "c8_dynamic", False) or not supported(entry):
         return entry
-    p = entry.args
-    need = workspace_bytes(p.tokens)
-    allocate = scratch_allocator or (
-        lambda name, shape, dtype, device: torch.empty(shape, dtype=dtype, device=device)
-    )
-    workspace = getattr(entry, 'workspace', None)
-    if shared_storage:
-        if workspace is None or workspace.numel() * workspace.element_size() < need:
-            raise ValueError('C8 shared controls require a workspace of workspace_bytes(tokens) bytes')
-    elif workspace is None or workspace.numel() * workspace.element_size() < need:
-        workspace = allocate('workspace', (need,), torch.uint8, entry.case.q.device)
+    device = entry.case.q.device
+    need = workspace_bytes(entry.args.tokens)
+    workspace = getattr(entry, "workspace", None)
+    large_enough = workspace is not None and workspace.numel() * workspace.element_size() >= need
+    if shared_storage and not large_enough:
+        raise ValueError("C8 shared controls require a workspace of workspace_bytes(tokens) bytes")
+    if not large_enough:
+        workspace = (scratch_allocator("workspace", (need,), torch.uint8, device) if scratch_allocator
+                     else torch.empty(need, dtype=torch.uint8, device=device))
     if workspace.data_ptr() % 256:
-        raise ValueError('Attention workspace must be 256-byte aligned')
-    partial = getattr(entry, 'partial', None)
+        raise ValueError("Attention workspace must be 256-byte aligned")
+    partial = getattr(entry, "partial", None)
     if partial is None:
-        partial = torch.empty(0, dtype=torch.float32, device=entry.case.q.device)
+        partial = torch.empty(0, dtype=torch.float32, device=device)       # kept for callers that read `.partial`
 
-    out = copy.copy(entry)
-    out.args = type(p).from_buffer_copy(p)
-    out.args.workspace = workspace.data_ptr()
-    out.args.partial = 0
-    out.args.splits = 1
-    out.workspace, out.partial = workspace, partial
-    out.blocks, out.splits = CORES, 1
-    out.argument_address = ctypes.addressof(out.args)
-    out._c8_library = library()
-    small = p.ratio == 4 and p.tokens < 24
-    suffix = 'sparse_small' if small else ('sparse' if p.ratio == 4 else 'dense')
-    out.launch = getattr(out._c8_library, 'launch_sharedkv_c8_' + suffix)
-    out.variant = 22 if small else (20 if p.ratio == 4 else 21)
-    out.native = native_host(os.environ.get('SHAREDKV_HOST_QUEUE') == '1')
-    if out.native is not None and out.native.attention_args_size != ctypes.sizeof(type(p)):
-        raise RuntimeError('C8 host/device argument ABI mismatch')
-    out.c8_dynamic = True
-    return out
+    bound = copy.copy(entry)
+    bound.args = type(entry.args).from_buffer_copy(entry.args)
+    bound.args.workspace, bound.args.partial, bound.args.splits = workspace.data_ptr(), 0, 1
+    bound.workspace, bound.partial = workspace, partial
+    bound.blocks, bound.splits = CORES, 1
+    bound.argument_address = ctypes.addressof(bound.args)
+    name = _launcher_name(bound.args)
+    bound._c8_library = library()
+    bound.launch = getattr(bound._c8_library, "launch_sharedkv_c8_" + name)
+    bound.variant = _VARIANTS[name]
+    bound.native = native_host(os.environ.get("SHAREDKV_HOST_QUEUE") == "1")
+    if bound.native is not None and bound.native.attention_args_size != ctypes.sizeof(type(bound.args)):
+        raise RuntimeError("C8 host/device argument ABI mismatch")
+    bound.c8_dynamic = True
+    return bound
 
 
 def host_module():
@@ -125,18 +128,16 @@ def host_module():
 
 @lru_cache(maxsize=2)
 def native_host(queued=False):
+    """attention / attention_queued of the host bridge behind one name (c8_attention.py:131-138)."""
     module = host_module()
     if module is None:
         return None
-    return SimpleNamespace(
-        attention=module.attention_queued if queued else module.attention,
-        attention_args_size=module.attention_args_size,
-        _owner=module,
-    )
+    call = module.attention_queued if queued else module.attention
+    return SimpleNamespace(attention=call, attention_args_size=module.attention_args_size, _owner=module)
 
 
 def launch_raw(entry):
     """ctypes path (SHAREDKV_USE_CTYPES=1): call the launcher symbol on the current stream."""
     with torch.cuda.device(entry.case.q.device):
-        check(entry.launch(entry.blocks, current_stream(entry.device_index), ctypes.byref(entry.args)),
-              'attention launch')
+        status = entry.launch(entry.blocks, current_stream(entry.device_index), ctypes.byref(entry.args))
+    check(status, "attention launch")
