@@ -52,29 +52,32 @@ def scratch_allocator(name, shape, dtype, device):
     stream gets its own.  Capacities are powers of two and superseded buffers are kept alive,
     because a captured graph may still point at them.
     """
-    key = device, stream_key(device), name, dtype
-    buffers = _scratch.setdefault(key, [])
-    count = math.prod(shape)
-    if not buffers or buffers[-1].numel() < count:
-        buffers.append(torch.empty(1 << max(count - 1, 0).bit_length(), dtype=dtype, device=device))
-    return buffers[-1][:count].view(shape)
+    elements = math.prod(shape)
+    generations = _scratch.setdefault((device, stream_key(device), name, dtype), [])
+    newest = generations[-1] if generations else None
+    if newest is None or newest.numel() < elements:
+        capacity = 1 << max(elements - 1, 0).bit_length()
+        newest = torch.empty(capacity, dtype=dtype, device=device)
+        generations.append(newest)
+    return newest[:elements].view(shape)
 
 
 @lru_cache(maxsize=1)
 def load_scales():
     """Frozen per-channel scales from the file named by SHAREDKV_SCALES (vllm_adapter.py:52-63):
     {"protocol": "sharedkv-c8-v1", "scales": {"<layer prefix>.<ori|cmp>": FP32[512] > 0}}."""
-    path = os.environ.get("SHAREDKV_SCALES")
-    if not path:
+    location = os.environ.get("SHAREDKV_SCALES", "")
+    if location == "":
         raise ValueError("INT8 mode requires SHAREDKV_SCALES containing frozen calibrated scales")
-    payload = torch.load(path, map_location="cpu", weights_only=True)
-    if payload.get("protocol") != SCALE_PROTOCOL:
+    stored = torch.load(location, map_location="cpu", weights_only=True)
+    if stored.get("protocol") != SCALE_PROTOCOL:
         raise ValueError("Wrong shared-KV scale protocol")
-    for key, value in payload["scales"].items():
-        good = value.shape == (512,) and value.dtype == torch.float32
-        if not good or not bool(torch.isfinite(value).all() & (value > 0).all()):
-            raise ValueError(f"Invalid scale vector: {key}")
-    return payload["scales"]
+    table = stored["scales"]
+    for name, vector in table.items():
+        shaped = tuple(vector.shape) == (512,) and vector.dtype == torch.float32
+        if not (shaped and bool(torch.isfinite(vector).all()) and bool((vector > 0).all())):
+            raise ValueError(f"Invalid scale vector: {name}")
+    return table
 
 
 @lru_cache(maxsize=16)
@@ -92,57 +95,57 @@ class LayerRuntime:
     by everything but the pointers (vllm_adapter.py:74-214)."""
 
     def __init__(self, impl):
-        self.impl = impl
-        self.prefix = impl.swa_cache_layer.prefix.removesuffix(".swa_cache")
         if impl.head_dim != 512 or getattr(impl, "turboquant", None) is not None:
             raise ValueError("INT8 shared-KV requires ordinary D=512 DSA")
         parallel = getattr(getattr(impl, "vllm_config", None), "parallel_config", None)
-        if (getattr(parallel, "decode_context_parallel_size", 1) != 1
-                or getattr(parallel, "prefill_context_parallel_size", 1) != 1):
+        context_parallel = [getattr(parallel, f"{phase}_context_parallel_size", 1) for phase in ("decode", "prefill")]
+        if context_parallel != [1, 1]:
             raise ValueError("Context-parallel cache writers have not been integrated")
-        self.scales = {}
-        self.writers = {}
-        self.attention_ops = OrderedDict()
-        self.captured_ops = []
-        self.captured_ids = set()
-        self.empty_lse = None
-        self.plan = None
+        self.impl = impl
+        self.prefix = impl.swa_cache_layer.prefix.removesuffix(".swa_cache")      # key prefix in the scale file
+        self.scales, self.writers = {}, {}                   # kind -> (scale, inverse); geometry -> prepared writer
+        self.attention_ops = OrderedDict()                   # geometry -> prepared attention, least recent first
+        self.captured_ops, self.captured_ids = [], set()     # operators whose launches sit in a captured graph
         self.reported_caches = set()
+        self.empty_lse = self.plan = None
 
     def scale(self, kind, device):
         """(scale, inverse scale) of this layer's `kind` cache on `device`; the inverse is rounded
         from the FP64 reciprocal as the cache writer expects (reference.py:48-50)."""
-        if kind not in self.scales:
+        pair = self.scales.get(kind)
+        if pair is None:
             check_device(device)
-            key = f"{self.prefix}.{kind}"
-            cpu = load_scales().get(key)
-            if cpu is None:
-                raise ValueError(f"Missing real-model calibration for {key}")
-            self.scales[kind] = (cpu.to(device), cpu.double().reciprocal().float().to(device))
-        return self.scales[kind]
+            name = f"{self.prefix}.{kind}"
+            frozen = load_scales().get(name)
+            if frozen is None:
+                raise ValueError(f"Missing real-model calibration for {name}")
+            inverse = frozen.to(torch.float64).reciprocal().to(torch.float32)
+            pair = self.scales[kind] = (frozen.to(device), inverse.to(device))
+        return pair
 
     def write(self, cache, updates, slots, kind):
         """Quantize `updates` with the layer's frozen scale and scatter them into `cache`."""
-        if updates is None or updates.shape[0] == 0:
+        rows = 0 if updates is None else updates.shape[0]
+        if rows == 0:
             return
-        if slots.shape[0] != updates.shape[0]:
+        if slots.shape[0] != rows:
             raise ValueError("Cache-write slot/update lengths differ")
-        # the cache allocation and the layouts are stable, the number of rows is not
-        key = (kind, geometry(cache), updates.shape[1:], updates.stride(), updates.dtype,
-               slots.shape[1:], slots.stride(), slots.dtype, updates.device, slots.device, stream_key(cache.device))
-        writer = self.writers.get(key)
-        if writer is None:
-            writer = PreparedCacheWrite(cache, updates, slots, self.scale(kind, cache.device)[1])
-            self.writers[key] = writer
-        else:
+        # a prepared writer is reused while everything but the pointers and the row count stays the same
+        layout = (kind, stream_key(cache.device), geometry(cache),
+                  updates.shape[1:], updates.stride(), updates.dtype, updates.device,
+                  slots.shape[1:], slots.stride(), slots.dtype, slots.device)
+        writer = self.writers.get(layout)
+        if writer is not None:
             writer._rebind_same_geometry(cache, updates, slots)
+        else:
+            writer = self.writers[layout] = PreparedCacheWrite(cache, updates, slots, self.scale(kind, cache.device)[1])
         writer.run()
+        # the launch is queued: same-stream lifetimes protect the tensors, no need to pin activations here
+        writer.updates = writer.slots = None
         if kind not in self.reported_caches:
+            self.reported_caches.add(kind)
             _log.info("Standalone INT8 sharedKV cache %s.%s: shape=%s dtype=%s page_stride=%d bytes",
                       self.prefix, kind, tuple(cache.shape), cache.dtype, cache.stride(0))
-            self.reported_caches.add(kind)
-        # same-stream lifetimes are enough after the launch; do not pin every layer's activations
-        writer.updates = writer.slots = None
 
     @staticmethod
     def _case_from_call(q, kw):
