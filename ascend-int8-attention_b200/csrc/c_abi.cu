@@ -3,6 +3,7 @@
 #include <stdint.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "../../include/sharedkv_c_abi.h"
 #include "sharedkv_internal.h"
@@ -14,7 +15,6 @@ namespace sharedkv {
 
 int device_sm_count()
 {
-    constexpr int kMaxDevices = 64;
     static std::atomic<int> cache[kMaxDevices];
     int device = -1;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0) return -1;
@@ -26,6 +26,17 @@ int device_sm_count()
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
     if (device < kMaxDevices) cache[device].store(sms, std::memory_order_relaxed);
     return sms;
+}
+
+// SHAREDKV_PDL=0 launches without the programmatic-stream-serialization attribute (the kernels'
+// griddepcontrol instructions are then no-ops).
+bool programmatic_launch_enabled()
+{
+    static const bool enabled = [] {
+        const char *v = getenv("SHAREDKV_PDL");
+        return !(v && v[0] == '0' && v[1] == 0);
+    }();
+    return enabled;
 }
 
 namespace {
@@ -59,7 +70,17 @@ extern "C" {
 uint32_t sharedkv_attention_args_size(void) { return (uint32_t)sizeof(SharedKVArgs); }
 uint32_t sharedkv_cache_args_size(void) { return (uint32_t)sizeof(CacheWriteArgs); }
 uint32_t sharedkv_attention_variant_count(void) { return SHAREDKV_VARIANT_C4_SMALL + 1; }
-uint64_t sharedkv_workspace_bytes(uint32_t tokens) { return sharedkv::workspace_bytes(tokens); }
+uint64_t sharedkv_workspace_bytes(uint32_t tokens) { return sharedkv::ws_bytes(tokens); }
+
+int sharedkv_workspace_init(void *workspace, void *stream)
+{
+    if (workspace == nullptr || reinterpret_cast<uintptr_t>(workspace) % 256u) return SHAREDKV_EINVAL;
+    return (int)cudaMemsetAsync(workspace, 0, sharedkv::kWsInitBytes, static_cast<cudaStream_t>(stream));
+}
+int sharedkv_workspace_status(const void *workspace, void *stream)
+{
+    return sharedkv::workspace_status(workspace, static_cast<cudaStream_t>(stream));
+}
 
 int launch_sharedkv_c8_sparse(uint32_t, void *stream, const SharedKVArgs *args)
 {
@@ -106,6 +127,7 @@ const char *sharedkv_status_string(int status)
         case SHAREDKV_EINVAL: return "invalid argument: null pointer, unsupported geometry or misaligned buffer";
         case SHAREDKV_ERANGE: return "batch or token count beyond what the workspace can plan";
         case SHAREDKV_EVARIANT: return "unknown attention kernel variant";
+        case SHAREDKV_ETIMEDOUT: return "a wait inside the decode kernel ran out; the results of that launch are invalid";
         default: break;
     }
     if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));

@@ -1,9 +1,17 @@
 // Paged INT8 KV-cache writer for sm_100a.
 //
-// One warp owns one update row: lane l converts channels [16 l, 16 l + 16), i.e. two
-// 16-byte BF16 loads in and one 16-byte INT8 store out, so a row is read as 32
-// coalesced 32-byte pieces and written as one coalesced 512-byte line.  The kernel
-// is pure streaming (1024 B read + 512 B written per row) and is bounded by HBM.
+// One warp owns one update row at a time: lane l converts channels [16 l, 16 l + 16), i.e. two
+// 16-byte BF16 loads in and one 16-byte INT8 store out, so a row is read as 32 coalesced 32-byte
+// pieces and written as one coalesced 512-byte line.  The kernel is pure streaming (1024 B read +
+// 512 B written per row) and is bounded by HBM; it lasts 5-20 microseconds, so what matters is how
+// soon the memory system is full and how few dependent round trips a warp makes:
+//   * a warp's slots are read once, up front, one row per lane (a warp owns rows w, w + W, ...),
+//     and handed round by shuffles;
+//   * row loads do not wait for the slots: four rows per warp are requested unconditionally, and
+//     only the store needs the slot (a row whose slot turns out to be invalid was read in vain);
+//   * the launch carries the programmatic-stream-serialization attribute, so its CTAs are resident
+//     and past their set-up when the previous kernel of the stream (often the other cache's
+//     writer) ends; nothing is read before griddepcontrol.wait returns.
 //
 // Arithmetic (per element, matching the reference's CPU quantizer
 // npu_sparse_attn_sharedkv_int8/reference.py:52-53 and the device writer
@@ -17,18 +25,19 @@
 #include <stdint.h>
 
 #include "../../include/sharedkv_c_abi.h"
+#include "ptx_sm100.cuh"
 #include "sharedkv_internal.h"
 
 namespace sharedkv {
 namespace {
 
+using ptx::grid_dependency_launch_dependents;
+using ptx::grid_dependency_wait;
+
 constexpr int kWriterThreads = 256;          // 8 warps
-#ifndef SHAREDKV_WRITER_ROWS
-#define SHAREDKV_WRITER_ROWS 3
-#define SHAREDKV_WRITER_CTAS 4
-#endif
-constexpr int kRowsInFlight = SHAREDKV_WRITER_ROWS;       // rows a warp keeps in flight per iteration
-constexpr int kWriterCtasPerSm = SHAREDKV_WRITER_CTAS;    // resident CTAs per SM the vector kernel is compiled for
+constexpr int kRowsInFlight = 4;             // rows a warp requests before it converts the first (divides 32)
+constexpr int kWriterCtasPerSm = 3;          // resident CTAs per SM the vector kernel is compiled for
+constexpr uint64_t kNoSlot = ~0ull;          // byte offset standing for "skip this row"
 
 __device__ __forceinline__ uint32_t quantize4(uint32_t lo2, uint32_t hi2, const float *inv)
 {
@@ -69,9 +78,29 @@ __device__ __forceinline__ bool resolve_slot(const CacheWriteArgs &p, uint32_t r
 template <class Index, bool Paired>
 __global__ void __launch_bounds__(kWriterThreads, kWriterCtasPerSm) cache_write_vec(const CacheWriteArgs p)
 {
+    grid_dependency_launch_dependents();
+    grid_dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kWriterThreads + threadIdx.x) >> 5;
     const uint32_t warps = (gridDim.x * kWriterThreads) >> 5;
+    if (warp >= p.tokens) return;
+    const uint32_t mine = (p.tokens - warp + warps - 1) / warps;          // rows warp, warp + warps, ... of this warp
+    const char *updates = reinterpret_cast<const char *>(p.updates);
+    char *cache = reinterpret_cast<char *>(p.cache);
+    const uint64_t row_bytes = p.updateStride * 2u;
+
+    uint4 a[kRowsInFlight], b[kRowsInFlight];
+    auto request = [&](uint32_t first) {                                 // rows first .. first + kRowsInFlight - 1 of this warp
+#pragma unroll
+        for (int i = 0; i < kRowsInFlight; ++i) {
+            if (first + i < mine) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(updates + (uint64_t)(warp + (first + i) * warps) * row_bytes) + lane * 2;
+                a[i] = __ldcs(src);
+                b[i] = __ldcs(src + 1);
+            }
+        }
+    };
+    request(0);
     float inv[16];
     {
         const float4 *s = reinterpret_cast<const float4 *>(p.inverseScale) + lane * 4;
@@ -81,31 +110,24 @@ __global__ void __launch_bounds__(kWriterThreads, kWriterCtasPerSm) cache_write_
             inv[4 * i] = v.x; inv[4 * i + 1] = v.y; inv[4 * i + 2] = v.z; inv[4 * i + 3] = v.w;
         }
     }
-    const char *updates = reinterpret_cast<const char *>(p.updates);
-    char *cache = reinterpret_cast<char *>(p.cache);
-    for (uint32_t base = warp; base < p.tokens; base += warps * kRowsInFlight) {
-        uint4 a[kRowsInFlight], b[kRowsInFlight];
-        uint64_t dst[kRowsInFlight];
-        bool live[kRowsInFlight];
+    for (uint32_t chunk = 0; chunk < mine; chunk += 32u) {
+        // lane j resolves the slot of the warp's row chunk + j
+        uint64_t my_dst = kNoSlot;
+        if (chunk + lane < mine && !resolve_slot<Index, Paired>(p, warp + (chunk + lane) * warps, my_dst)) my_dst = kNoSlot;
+        const uint32_t in_chunk = min(32u, mine - chunk);
+        for (uint32_t k = 0; k < in_chunk; k += kRowsInFlight) {
+            if (chunk + k != 0) request(chunk + k);
 #pragma unroll
-        for (int i = 0; i < kRowsInFlight; ++i) {
-            const uint32_t row = base + i * warps;
-            live[i] = row < p.tokens && resolve_slot<Index, Paired>(p, row, dst[i]);
-            if (live[i]) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(updates + (uint64_t)row * p.updateStride * 2u) + lane * 2;
-                a[i] = __ldcs(src);
-                b[i] = __ldcs(src + 1);
+            for (int i = 0; i < kRowsInFlight; ++i) {
+                const uint64_t dst = __shfl_sync(0xffffffffu, my_dst, (k + i) & 31u);
+                if (k + i >= in_chunk || dst == kNoSlot) continue;
+                uint4 o;
+                o.x = quantize4(a[i].x, a[i].y, inv);
+                o.y = quantize4(a[i].z, a[i].w, inv + 4);
+                o.z = quantize4(b[i].x, b[i].y, inv + 8);
+                o.w = quantize4(b[i].z, b[i].w, inv + 12);
+                *reinterpret_cast<uint4 *>(cache + dst + lane * 16u) = o;
             }
-        }
-#pragma unroll
-        for (int i = 0; i < kRowsInFlight; ++i) {
-            if (!live[i]) continue;
-            uint4 o;
-            o.x = quantize4(a[i].x, a[i].y, inv);
-            o.y = quantize4(a[i].z, a[i].w, inv + 4);
-            o.z = quantize4(b[i].x, b[i].y, inv + 8);
-            o.w = quantize4(b[i].z, b[i].w, inv + 12);
-            *reinterpret_cast<uint4 *>(cache + dst[i] + lane * 16u) = o;
         }
     }
 }
@@ -115,6 +137,8 @@ __global__ void __launch_bounds__(kWriterThreads, kWriterCtasPerSm) cache_write_
 template <class Index, bool Paired>
 __global__ void __launch_bounds__(kWriterThreads) cache_write_scalar(const CacheWriteArgs p)
 {
+    grid_dependency_launch_dependents();
+    grid_dependency_wait();
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warp = (blockIdx.x * kWriterThreads + threadIdx.x) >> 5;
     const uint32_t warps = (gridDim.x * kWriterThreads) >> 5;
@@ -148,9 +172,17 @@ cudaError_t launch_variant(const CacheWriteArgs &a, bool vec, cudaStream_t strea
     const uint32_t cap = (uint32_t)sms * (vec ? (uint32_t)kWriterCtasPerSm : 8u);
     if (blocks > cap) blocks = cap;
     if (blocks == 0) return cudaSuccess;
-    if (vec) cache_write_vec<Index, Paired><<<blocks, kWriterThreads, 0, stream>>>(a);
-    else cache_write_scalar<Index, Paired><<<blocks, kWriterThreads, 0, stream>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(blocks);
+    config.blockDim = dim3(kWriterThreads);
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = programmatic_launch_enabled() ? 1u : 0u;
+    return vec ? cudaLaunchKernelEx(&config, cache_write_vec<Index, Paired>, a)
+               : cudaLaunchKernelEx(&config, cache_write_scalar<Index, Paired>, a);
 }
 
 }  // namespace

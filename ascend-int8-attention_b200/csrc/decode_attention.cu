@@ -1,8 +1,12 @@
 // INT8 shared-KV decode attention for sm_100a (C4: top-k compressed rows + window,
 // C128: every compressed row + window), eight heads, D = 512.
 //
-// One call = a memset of the small plan area of the workspace (split-K tickets, status word) and
-// one kernel launch, both on the caller's stream.
+// One call = one kernel launch on the caller's stream (no memset, no second kernel): the split-K
+// tickets in the workspace are zero between launches because the CTA that merges a token puts its
+// ticket back, and the status word is sticky.  The launch carries the programmatic-stream-
+// serialization attribute: its CTAs may become resident while the previous kernel of the stream
+// drains, set up barriers and tensor memory, and wait (griddepcontrol.wait) for that kernel to
+// finish before they read or write any global memory.
 //
 //   decode_kernel  one persistent CTA per SM, 24 warps in six roles that meet only at mbarriers.
 //     set-up       every CTA derives the live batch / token count from cuQ and seqLens (trailing
@@ -34,13 +38,19 @@
 //   p_hi = rint(127 w), p_lo = rint((127 w - p_hi) * 127)
 //   acc = acc r + (float(O_hi) + float(O_lo) * (1/127)) * scale_kind * (1/127)
 //   state starts at m = sink, l = 1 (first piece) or 0;  out = bf16(sum g acc / sum g l), g = exp(m - max m)
-// Every FP32 operation is a separately rounded IEEE operation (no FMA contraction).
+// The logits and the P codes follow that operation order exactly (separately rounded multiplies and
+// adds).  Four places fuse or reorder, each within one FP32 ulp of the reference's order:
+//   l = fma(l, r, w)  per key instead of  l r + sum w;   scale * (1/127) folded into one constant;
+//   (O_hi + O_lo/127) and acc + pv * scale evaluated as two FMAs;   out = acc * (1/l) with a
+//   correctly rounded reciprocal instead of a division.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include <atomic>
+#include <cstddef>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/sharedkv_c_abi.h"
@@ -53,8 +63,8 @@ namespace {
 using namespace ptx;
 
 // ------------------------------------------------------------------ geometry
-constexpr uint32_t kHeads = 8, kDim = 512, kWindow = 128, kPage = 32;
-constexpr uint32_t kTileKeys = 128;
+constexpr uint32_t kWindow = 128, kPage = 32;
+constexpr uint32_t kTileKeys = split::kTileKeys;
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kTileBytes = kTileKeys * kDim;            // 65536
 constexpr uint32_t kSegBytes = kTileKeys * 128;              // one 128-channel segment of a tile: 16384
@@ -65,25 +75,22 @@ constexpr uint32_t kWarpProducerB = 20;                  // warps 12-15 fetch th
 // Registers per thread by role (the kernel starts every warp at 80; see registers_release/acquire).
 // Per SM sub-partition: 2 softmax + 1 accumulate + 2 producer + 1 MMA-or-query warp share 6 x 80 x 32 registers.
 constexpr uint32_t kRegsLaunch = 80;     // what __launch_bounds__(768, 1) lets the compiler use
-#ifndef SHAREDKV_REGS_SOFTMAX
-#define SHAREDKV_REGS_SOFTMAX 80
-#define SHAREDKV_REGS_ACCUMULATE 128
-#define SHAREDKV_REGS_PRODUCER 56
-#define SHAREDKV_REGS_ISSUE 80
-#endif
-constexpr uint32_t kRegsSoftmax = SHAREDKV_REGS_SOFTMAX, kRegsAccumulate = SHAREDKV_REGS_ACCUMULATE,
-                   kRegsProducer = SHAREDKV_REGS_PRODUCER, kRegsIssue = SHAREDKV_REGS_ISSUE;
+constexpr uint32_t kRegsSoftmax = 80, kRegsAccumulate = 128, kRegsProducer = 56, kRegsIssue = 80;
 // The registers a CTA may re-divide are those it was launched with.  Asking for more than that
 // would leave registers_acquire waiting for ever.
 static_assert(2 * kRegsSoftmax + kRegsAccumulate + 2 * kRegsProducer + kRegsIssue <= 6 * kRegsLaunch,
               "register budgets of one sub-partition's six warps exceed the launch allocation");
 static_assert(kRegsSoftmax >= kRegsLaunch && kRegsAccumulate >= kRegsLaunch && kRegsProducer <= kRegsLaunch && kRegsIssue <= kRegsLaunch,
               "acquire only grows, release only shrinks");
-constexpr uint32_t kMaxCtas = 160;
-constexpr uint32_t kPartialFloats = kHeads * kDim + 16;      // acc[8][512], m[8], l[8]
+constexpr uint32_t kMaxCtas = split::kMaxCtas;
 constexpr float kInv127 = (float)(1.0 / 127);
 constexpr float kMasked = -1e30f;
-constexpr long long kWaitCycles = 4000000000ll;              // ~2 s: a wait that long is a failure, not a stall
+constexpr uint32_t kWaitMillionCycles = 4000;                // ~2 s: a wait that long is a failure, not a stall
+constexpr uint32_t kWaitMillionCyclesTest = 2;               // ~1 ms: the limit the wait-timeout test asks for
+constexpr uint32_t kDrainNanoseconds = 200000;               // after a timeout: time given to copies and MMAs in flight
+// SharedKVDebug.reserved: bits 0-15 cap the number of CTAs, bit 31 selects the cp.async row gather,
+// bit 30 makes one barrier arrival go missing under a ~1 ms wait limit (the status-word test).
+constexpr uint32_t kDebugCtaCapMask = 0xffffu, kDebugLegacyGather = 0x80000000u, kDebugShortWaits = 0x40000000u;
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kSmKv = 0;
@@ -102,8 +109,8 @@ constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kB
                    kBarOFree = 14, kBarQReady = 16 /* x3 query buffers */, kBarQFree = 19 /* x3 */,
                    kBarGroup = 22 /* x4: softmax halves, all softmax, all accumulate */,
                    kBarRescale = 26 /* x8 */, kBarItemDone = 34 /* x8 */, kNumBars = 42;
-constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words
-constexpr uint32_t kSmemBytes = kSmMisc + 16 + 1024;         // + alignment slack
+constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words, wait limit
+constexpr uint32_t kSmemBytes = kSmMisc + 32 + 1024;         // + alignment slack
 static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
 
 // tensor-memory columns
@@ -111,37 +118,19 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kColS = 0;     // S[b] at 16 b
 constexpr uint32_t kColO = 64;    // O[b] at 64 + 64 b, four 16-column channel blocks each
 
-// workspace map
+// workspace (the byte map is in sharedkv_internal.h)
 struct PlanHeader {
     uint32_t live_batch, live_tokens, total_tiles, quota, n_items, status, grid, pad;
 };
+static_assert(offsetof(PlanHeader, status) == kWsStatus, "status word offset is part of the library's interface");
 struct Item {
     uint32_t token, batch;
     int32_t position;
     uint32_t tile_begin, tile_end, part, nparts, first_cta;
 };
 static_assert(sizeof(Item) == 32, "work item is two 16-byte loads");
-// bytes 0-63: PlanHeader; 64-1023 and the 4 x tokens bytes in front of the tickets are kept free (the
-// size formula is part of the ABI: sharedkv_workspace_bytes and its Python mirror)
-constexpr uint64_t kWsItems = 1024;
-__host__ __device__ inline uint64_t ws_tile_start(uint32_t tokens) { return kWsItems + 32ull * (tokens + kMaxCtas); }
-__host__ __device__ inline uint64_t ws_tickets(uint32_t tokens) { return ws_tile_start(tokens) + 4ull * tokens; }
-__host__ __device__ inline uint64_t ws_partials(uint32_t tokens)
-{
-    return (ws_tickets(tokens) + 4ull * tokens + 255ull) & ~255ull;
-}
-
-enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1 };
 
 // ------------------------------------------------------------------ small helpers
-__device__ __forceinline__ uint32_t tiles_of_token(int ratio, int32_t position, uint32_t topk)
-{
-    if (position < 0) return 1;
-    const uint32_t count = (uint32_t)(position + 1) / (uint32_t)ratio;
-    if (ratio == 4) return 1 + (count ? (topk + kTileKeys - 1) / kTileKeys : 0);
-    return 1 + (count + kTileKeys - 1) / kTileKeys;
-}
-
 __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, uint32_t lane)
 {
 #pragma unroll
@@ -173,10 +162,6 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
 }
 
 // ------------------------------------------------------------------ work split
-#ifndef SHAREDKV_ITEM_COST
-#define SHAREDKV_ITEM_COST 1
-#endif
-constexpr uint32_t kItemCost = SHAREDKV_ITEM_COST;      // cost of a token's once-only work, in tiles
 constexpr uint32_t kPlanStaged = 11776;      // cuQ entries kept in shared memory (46 KB)
 
 // Request that owns query token t: the b with cu[b] <= t < cu[b + 1], 0 <= b < live_batch.
@@ -191,10 +176,10 @@ __device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_ba
 }
 
 // Work split, computed by every CTA for itself at the start of the decode kernel (all threads take
-// part).  The live shape comes from cuQ / seqLens on the device, so a captured graph follows the
-// live batch.  Every live token has 1 + ceil(compressed rows / 128) tiles; the flat tile list is cut
-// into `grid` equal ranges; the pieces of tokens that fall into this CTA's range become its items,
-// written to workspace entries no other CTA uses (entry = token + CTA number).  `scratch` is shared memory the roles do not use yet (the KV ring).
+// part); the arithmetic is in work_split.h.  The live shape comes from cuQ / seqLens on the device,
+// so a captured graph follows the live batch.  The pieces of tokens that fall into this CTA's range
+// of the flat tile list become its items, written to workspace entries no other CTA uses.
+// `scratch` is shared memory the roles do not use yet (the KV ring).
 struct PlanResult {
     uint32_t first, end, live_tokens;
 };
@@ -221,15 +206,14 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     const int32_t *cu = staged ? sc->cu : cu_global;
     uint32_t live = 0, mismatch = 0xffffffffu;
     for (uint32_t b = tid; b < p.batch; b += kThreads) {
-        if ((b == tid ? seq_first : seq[b]) > 0 && cu[b + 1] >= 0) live = b + 1;
+        if (split::request_is_live(b == tid ? seq_first : seq[b], cu[b + 1])) live = b + 1;
         if (cu[b + 1] != (int32_t)(b + 1) && mismatch == 0xffffffffu) mismatch = b;
     }
     if (live) atomicMax(&sc->live, live);
     if (mismatch != 0xffffffffu) atomicMin(&sc->mismatch, mismatch);
     __syncthreads();
     const uint32_t live_batch = sc->live;
-    int32_t end = live_batch ? cu[live_batch] : 0;
-    const uint32_t live_tokens = end <= 0 ? 0u : ((uint32_t)end < p.tokens ? (uint32_t)end : p.tokens);
+    const uint32_t live_tokens = split::live_token_count(live_batch ? cu[live_batch] : 0, p.tokens);
     // one query token per request (plain decode): token t belongs to request t
     const bool one_each = live_tokens == live_batch && cu[0] == 0 && sc->mismatch >= live_batch;
 
@@ -239,8 +223,8 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     const uint32_t t_begin = min(tid * per, live_tokens), t_end = min(t_begin + per, live_tokens);
     auto tiles_of = [&](uint32_t t, uint32_t &batch, int32_t &position) {
         batch = one_each ? t : owner_of(cu, live_batch, t);
-        position = seq[batch] - (cu[batch + 1] - (int32_t)t);
-        return tiles_of_token(RATIO, position, p.topk);
+        position = split::token_position(seq[batch], cu[batch + 1], t);
+        return split::tiles_of_token(RATIO, position, p.topk);
     };
     uint32_t my_tiles = 0;
     for (uint32_t t = t_begin; t < t_end; ++t) {
@@ -249,36 +233,31 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     }
     uint32_t total_tiles;
     const uint32_t tile_base = block_exclusive_scan(my_tiles, sc->scan, total_tiles);
-    // The ranges are cut in units of cost, not of tiles: a token costs its tiles plus kItemCost units
-    // for what happens once per token (query encode, final normalisation and store), placed in front
-    // of its first tile.  Tile j of token t sits at cost position (tiles before t) + kItemCost (t + 1) + j.
-    const uint32_t total_cost = total_tiles + kItemCost * live_tokens;
-    const uint32_t quota = total_cost ? (total_cost + grid - 1) / grid : 1;
+    const uint32_t quota = split::quota_of(split::total_cost(total_tiles, live_tokens), grid);
     const uint32_t me = blockIdx.x;
 
-    // This CTA's flat tile range is [me * quota, (me + 1) * quota).  The tokens that overlap it are
-    // consecutive, so an item needs no second scan for its place: the piece of token t that belongs
-    // to CTA c is stored at index t + c, which is unique and increasing along (token, piece) because
-    // a token's pieces sit in consecutive CTAs and the next token starts in the last of them or later.
-    uint32_t start = tile_base + kItemCost * t_begin;
-    if (start < (me + 1) * quota && start + my_tiles + kItemCost * (t_end - t_begin) > me * quota) {
+    // Only threads whose tokens overlap this CTA's range [me * quota, (me + 1) * quota) go on.
+    const uint32_t range_begin = split::first_tile_position(tile_base, t_begin) - split::kItemCost;
+    const uint32_t range_end = split::first_tile_position(tile_base + my_tiles, t_end) - split::kItemCost;
+    if (range_begin < (me + 1) * quota && range_end > me * quota) {
+        uint32_t before = tile_base;
         for (uint32_t t = t_begin; t < t_end; ++t) {
             uint32_t batch; int32_t position;
             const uint32_t n = tiles_of(t, batch, position);
-            start += kItemCost;
-            const uint32_t c0 = start / quota, pieces = (start + n - 1) / quota - c0 + 1;
-            if (me >= c0 && me < c0 + pieces) {
-                const uint32_t lo_flat = max(start, me * quota), hi_flat = min(start + n, (me + 1) * quota);
-                uint4 *dst = reinterpret_cast<uint4 *>(items + t + me);
-                dst[0] = make_uint4(t, batch, (uint32_t)position, lo_flat - start);
-                dst[1] = make_uint4(hi_flat - start, me - c0, pieces, c0);
-                atomicMin(&sc->first, t + me);
+            const uint32_t start = split::first_tile_position(before, t);
+            const split::Pieces pc = split::pieces_of(start, n, quota);
+            if (me >= pc.first_cta && me < pc.first_cta + pc.count) {
+                const split::TileRange r = split::piece_range(start, n, quota, me);
+                const uint32_t entry = split::item_index(t, me);
+                uint4 *dst = reinterpret_cast<uint4 *>(items + entry);
+                dst[0] = make_uint4(t, batch, (uint32_t)position, r.begin);
+                dst[1] = make_uint4(r.end, me - pc.first_cta, pc.count, pc.first_cta);
+                atomicMin(&sc->first, entry);
                 atomicAdd(&sc->count, 1u);
             }
-            start += n;
+            before += n;
         }
     }
-    const uint32_t item_carry = live_tokens;      // header only: tokens, not counting the extra pieces
     __syncthreads();
     PlanResult r;
     r.first = sc->count ? sc->first : 0u;
@@ -287,7 +266,7 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     if (me == 0 && tid == 0) {
         PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
         header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
-        header->quota = quota; header->n_items = item_carry; header->grid = grid;
+        header->quota = quota; header->n_items = live_tokens; header->grid = grid;
     }
     __syncthreads();          // the scratch area is handed back to the KV ring
     return r;
@@ -300,18 +279,7 @@ struct Shared {
     __device__ __forceinline__ volatile uint32_t *misc() const { return reinterpret_cast<volatile uint32_t *>(ptr + kSmMisc); }
 };
 
-#ifdef SHAREDKV_TIMING
-// Development aid (not built by default): cycles spent waiting, per CTA, per role and barrier.
-__device__ unsigned long long g_wait_cycles[kMaxCtas][450];
-__device__ __forceinline__ void timing_add(uint32_t slot, long long cycles)
-{
-    const uint32_t warp = threadIdx.x >> 5;
-    if ((threadIdx.x & 31u) == 0 && ((warp & 3u) == 0 || (warp >= 16 && warp < 20)))
-        atomicAdd(&g_wait_cycles[blockIdx.x][(warp < 16 ? (warp >> 2) : warp < 20 ? warp - 12u : 8u) * 50u + slot], (unsigned long long)cycles);
-}
-#endif
-
-// Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s.  The common case, a
+// Wait for a phase; gives up (and raises the CTA-wide abort flag) after ~2 s (misc[4], in millions of cycles).  The common case, a
 // phase that is already complete, is one instruction inline; the polling loop lives out of line so
 // that the many call sites stay small (the kernel's hot loops have to share the instruction cache).
 // ROLE (0 softmax, 1 accumulate, 2 producer, 3 issue/query) only makes one copy per register budget:
@@ -325,7 +293,7 @@ __device__ __noinline__ bool wait_phase_slow(uint32_t bar, uint32_t parity, vola
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 0) {
             if (misc[1]) return false;
-            if (clock64() - start > kWaitCycles) { misc[1] = 1; return false; }
+            if (clock64() - start > (long long)misc[4] * 1000000ll) { misc[1] = 1; return false; }
         }
     }
 }
@@ -333,21 +301,8 @@ template <int ROLE>
 __device__ __forceinline__ bool wait_phase(const Shared &sm, uint32_t bar_index, uint32_t parity)
 {
     const uint32_t bar = sm.bar(bar_index);
-#ifdef SHAREDKV_TIMING
-    struct Scope { uint32_t i; long long t0; __device__ ~Scope() { timing_add(i, clock64() - t0); } } scope{bar_index, clock64()};
-#endif
     if (mbar_try_wait(bar, parity)) return true;
     return wait_phase_slow<ROLE>(bar, parity, sm.misc());
-}
-
-__device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
-{
-    const uint4 *src = reinterpret_cast<const uint4 *>(items + index);
-    const uint4 a = src[0], b = src[1];
-    Item it;
-    it.token = a.x; it.batch = a.y; it.position = (int32_t)a.z; it.tile_begin = a.w;
-    it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
-    return it;
 }
 
 // Swizzled (128-byte) location of 16-byte chunk `chunk` (0..31) of row `row` in a
@@ -379,6 +334,11 @@ __device__ __forceinline__ Item decode_item(const uint4 &a, const uint4 &b)
     it.token = a.x; it.batch = a.y; it.position = (int32_t)a.z; it.tile_begin = a.w;
     it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
     return it;
+}
+__device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
+{
+    const uint4 *src = reinterpret_cast<const uint4 *>(items + index);
+    return decode_item(src[0], src[1]);
 }
 __device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items)
 {
@@ -548,12 +508,9 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 // Row fetch: one TMA gather of four consecutive slots x one 128-channel segment per lane
 // (lane = 4 * group + segment); for the compressed rows of a C128 layer, which fill whole pages,
 // four 4 KB page-segment boxes per warp; 16-byte cp.async copies when the page strides rule TMA out.
-#ifndef SHAREDKV_LOOKAHEAD
-#define SHAREDKV_LOOKAHEAD 1
-#endif
 // One tile of the set (= two tiles of the CTA, about 4 us) covers the latency of either read; a
 // deeper pipeline only lengthens the start of the kernel (measured: 2 is 3 % slower than 1).
-constexpr int kLookahead = SHAREDKV_LOOKAHEAD;
+constexpr int kLookahead = 1;
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
 template <int RATIO, bool TMA>
@@ -600,7 +557,9 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 int32_t id = kRowsInMap;
                 if (o >= 0) {
                     const bool ori = (o >> 8) & 1;
-                    if (!(ori && (uint32_t)pg >= p.oriPages))         // never read outside the original cache
+                    // never read outside the original cache; the compressed cache's page count is not
+                    // part of the argument struct, so only negative ids can be refused there
+                    if (ori ? (uint32_t)pg < p.oriPages : pg >= 0)
                         id = !TMA ? (int32_t)(((uint32_t)pg << 5) + ((uint32_t)o & 31u))       // page, row in page
                              : (RATIO == 128 && !ori)
                                  ? pg                                                          // whole-page fetch
@@ -615,7 +574,9 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 const uint32_t limit = ori ? 0x7fffffffu
                                            : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
                 const int32_t c = cand[u];
-                if (c >= 0 && (uint32_t)c < limit) {
+                // a row beyond the request's page-table row is no key (a sequence length larger
+                // than the table can describe must not read the next request's entries)
+                if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
                     off_b = (c & 31) | (ori ? 256 : 0);
                     page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
                                  : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
@@ -747,9 +708,6 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
             const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
             const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : cbuf * 8192u);
             const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
-#ifdef SHAREDKV_TIMING
-            const long long t_issue = clock64();
-#endif
             // the address field counts 16-byte units; offsets stay inside the 14-bit field
 #pragma unroll 1
             for (uint32_t seg = 0; seg < 4; ++seg) {
@@ -759,14 +717,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
                         mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 2048u + part * 32u) >> 4),
                                kIdescQK, seg | part);
             }
-#ifdef SHAREDKV_TIMING
-            const long long t_commit = clock64();
-            timing_add(44, t_commit - t_issue);
-#endif
             if (leader) mma_commit(sm.bar(kBarSFull + buf));
-#ifdef SHAREDKV_TIMING
-            timing_add(45, clock64() - t_commit);
-#endif
             if (leader) {
                 if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
                 else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
@@ -777,7 +728,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
     }
 }
 
-__device__ void mma_pv_loop(const Shared &sm, const uint32_t *, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+__device__ void mma_pv_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
 {
     constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
     // only the number of tiles matters here
@@ -1075,7 +1026,8 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 g[2u + half] = c_lo;
             }
             fence_proxy_async_smem();
-            mbar_arrive(sm.bar(kBarPReady + buf));
+            // wait-timeout test: the first tile's P codes are never announced
+            if (!(DEBUG && (dbg.reserved & kDebugShortWaits) && gt == 0)) mbar_arrive(sm.bar(kBarPReady + buf));
         }
 
         // denominators: sum the per-thread partial sums, hand (m, l) to the accumulate warps
@@ -1119,7 +1071,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
     const uint32_t warp = ch >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
     char *ws = reinterpret_cast<char *>(p.workspace);
-    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + ws_tickets(p.tokens));
+    uint32_t *tickets = reinterpret_cast<uint32_t *>(ws + kWsTickets);
     float *partials = reinterpret_cast<float *>(ws + ws_partials(p.tokens));
     volatile uint32_t *misc = sm.misc();
     uint32_t group_phase = 0;
@@ -1222,7 +1174,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         }
 
         // ---------------- piece of a token shared with other CTAs
-        const uint32_t my_slot = it.part == 0 ? it.first_cta * 2u + 1u : (it.first_cta + it.part) * 2u;
+        const uint32_t my_slot = split::partial_slot(it.first_cta, it.part);
         float *mine = partials + (uint64_t)my_slot * kPartialFloats;
 #pragma unroll
         for (int h = 0; h < 8; ++h)
@@ -1231,16 +1183,19 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         if (ch < 16) mine[4096 + ch] = fin[ch];
         __threadfence();
         if (!group_sync<1>(sm, 3, group_phase)) return;
-        if (ch == 0) misc[3] = atomicAdd(tickets + it.token, 1u);
+        if (ch == 0) misc[3] = atomicAdd(tickets + split::ticket_index(it.first_cta), 1u);
         if (!group_sync<1>(sm, 3, group_phase)) return;
         const uint32_t ticket = misc[3];
         if (ticket + 1u == it.nparts) {
+            // last piece to arrive: merge, and leave the ticket at zero for the next launch (nobody
+            // else touches it any more in this one)
+            if (ch == 0) tickets[split::ticket_index(it.first_cta)] = 0u;
             __threadfence();
             float top[8], den[8];
 #pragma unroll
             for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
             for (uint32_t q = 0; q < it.nparts; ++q) {
-                const uint32_t sl = q == 0 ? it.first_cta * 2u + 1u : (it.first_cta + q) * 2u;
+                const uint32_t sl = split::partial_slot(it.first_cta, q);
                 const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
@@ -1250,7 +1205,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
                 for (int h = 0; h < 8; ++h) acc[mb][h] = 0.f;
             for (uint32_t q = 0; q < it.nparts; ++q) {
-                const uint32_t sl = q == 0 ? it.first_cta * 2u + 1u : (it.first_cta + q) * 2u;
+                const uint32_t sl = split::partial_slot(it.first_cta, q);
                 const float *ps = partials + (uint64_t)sl * kPartialFloats;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
@@ -1308,6 +1263,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         for (uint32_t b = 0; b < 3; ++b) { mbar_init(sm.bar(kBarQReady + b), 32); mbar_init(sm.bar(kBarQFree + b), 1); }
         for (uint32_t i = 0; i < 8; ++i) { mbar_init(sm.bar(kBarRescale + i), 2); mbar_init(sm.bar(kBarItemDone + i), 2); }
         misc[1] = 0; misc[2] = 0; misc[3] = 0;
+        misc[4] = (DEBUG && (dbg.reserved & kDebugShortWaits)) ? kWaitMillionCyclesTest : kWaitMillionCycles;
         fence_mbar_init();
     }
     if (warp == kWarpMma) {
@@ -1318,9 +1274,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = misc[0];
-#ifdef SHAREDKV_TIMING
-    const long long kernel_start = clock64();
-#endif
+    // Everything above touched only this CTA's shared and tensor memory.  From here on global memory
+    // is read and written, which the previous kernel of the stream may still be producing or using
+    // (a query projection, the cache writer, an attention launch that shares this workspace).
+    grid_dependency_launch_dependents();
+    grid_dependency_wait();
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
@@ -1353,17 +1311,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
             // the whole warp runs the issue loop and one elected lane issues: with converged control
             // flow the operand descriptors live in uniform registers, which halves the cost per MMA
             if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
-            else mma_pv_loop(sm, nullptr, items, first, end, tmem);
+            else mma_pv_loop(sm, items, first, end, tmem);
             __syncwarp();
         }
     }
-#ifdef SHAREDKV_TIMING
-    timing_add(49, clock64() - kernel_start);
-#endif
     tc_fence_before();
     __syncthreads();
-    if (tid == 0 && misc[1])
-        reinterpret_cast<PlanHeader *>(const_cast<char *>(ws))->status = kStatusWaitTimeout;
+    if (misc[1]) {
+        // A wait ran out: every role has returned.  Row fetches and MMAs that were already issued
+        // may still be writing this CTA's shared and tensor memory, so the CTA stays for a while
+        // (far longer than a DRAM round trip) before it gives them up.  The status word is sticky.
+        if (tid == 0) reinterpret_cast<PlanHeader *>(const_cast<char *>(ws))->status = kStatusWaitTimeout;
+        for (uint32_t waited = 0; waited < kDrainNanoseconds; waited += 1000u) __nanosleep(1000u);
+        __syncthreads();
+    }
     if (warp == kWarpMma) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -1418,6 +1379,31 @@ bool make_page_map(CUtensorMap *map, uint64_t base, uint64_t page_stride)
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The tensor maps of a launch depend only on the cache base addresses and the compressed page
+// stride, which a serving layer keeps for its lifetime; encoding them costs microseconds of host
+// time per call.  Each host thread keeps the maps of the layers it launched last in a small
+// direct-mapped table (thread-local: no lock, no allocation); a miss encodes and replaces.
+struct MapSet {
+    uint64_t ori, cmp, cmp_stride;      // key; ori == 0 marks an empty entry
+    bool with_page_map;
+    CUtensorMap ori_map, cmp_map, cmp_page_map;
+};
+constexpr uint32_t kMapSets = 128;
+const MapSet *tensor_maps(uint64_t ori, uint64_t cmp, uint64_t cmp_stride, bool with_page_map)
+{
+    static thread_local MapSet table[kMapSets];
+    const uint64_t mixed = (ori >> 9) * 0x9e3779b97f4a7c15ull ^ (cmp >> 9) * 0xc2b2ae3d27d4eb4full ^ cmp_stride;
+    MapSet &e = table[(mixed >> 40) % kMapSets];
+    if (e.ori == ori && e.cmp == cmp && e.cmp_stride == cmp_stride && e.with_page_map == with_page_map) return &e;
+    e.ori = 0;
+    memset(&e.cmp_page_map, 0, sizeof(e.cmp_page_map));
+    if (!make_row_map(&e.ori_map, ori) || !make_row_map(&e.cmp_map, cmp) ||
+        (with_page_map && !make_page_map(&e.cmp_page_map, cmp, cmp_stride)))
+        return nullptr;
+    e.ori = ori; e.cmp = cmp; e.cmp_stride = cmp_stride; e.with_page_map = with_page_map;
+    return &e;
+}
+
 template <int RATIO, bool DEBUG, bool TMA>
 cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const CUtensorMap &ori_map,
                           const CUtensorMap &cmp_map, const CUtensorMap &cmp_page_map, uint32_t grid,
@@ -1425,39 +1411,45 @@ cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const C
 {
     // the opt-in to > 48 KB of dynamic shared memory is per device and per kernel
     static std::atomic<uint64_t> configured{0};
-    const uint64_t bit = 1ull << (device & 63);
-    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+    const bool cached = device >= 0 && device < kMaxDevices;
+    const uint64_t bit = cached ? 1ull << device : 0ull;
+    if (!cached || !(configured.load(std::memory_order_relaxed) & bit)) {
         cudaError_t e = cudaFuncSetAttribute(decode_kernel<RATIO, DEBUG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kSmemBytes);
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_relaxed);
     }
-    decode_kernel<RATIO, DEBUG, TMA><<<grid, kThreads, kSmemBytes, stream>>>(a, d, ori_map, cmp_map, cmp_page_map);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = programmatic_launch_enabled() ? 1u : 0u;
+    return cudaLaunchKernelEx(&config, decode_kernel<RATIO, DEBUG, TMA>, a, d, ori_map, cmp_map, cmp_page_map);
 }
 
 template <int RATIO>
 int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debug, int sms)
 {
     uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
-    const uint32_t cap = debug ? (debug->reserved & 0x7fffffffu) : 0u;      // test hook: fewer CTAs
+    const uint32_t cap = debug ? (debug->reserved & kDebugCtaCapMask) : 0u;      // test hook: fewer CTAs
     if (cap && cap < grid) grid = cap;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
     // Row gathers by TMA need page strides that are whole rows and row ids that fit the map;
     // anything else takes the cp.async producer.
-    CUtensorMap ori_map, cmp_map, cmp_page_map;
-    bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 && !(debug && (debug->reserved & 0x80000000u)) &&
+    static const CUtensorMap no_map = {};
+    bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 && !(debug && (debug->reserved & kDebugLegacyGather)) &&
                (uint64_t)a.oriPages * (a.oriStride / kDim) < (uint64_t)kRowsInMap && a.cmpStride / kDim < 65536;
-    memset(&cmp_page_map, 0, sizeof(cmp_page_map));
-    if (tma) tma = make_row_map(&ori_map, a.ori) && make_row_map(&cmp_map, a.cmp) &&
-                   (RATIO != 128 || make_page_map(&cmp_page_map, a.cmp, a.cmpStride));
-    if (!tma) { memset(&ori_map, 0, sizeof(ori_map)); memset(&cmp_map, 0, sizeof(cmp_map)); }
-    // The split-K tickets and the status word start every launch at zero; everything else in the
-    // workspace is written by the kernel before it is read.
-    e = cudaMemsetAsync(reinterpret_cast<void *>(a.workspace), 0, ws_partials(a.tokens), stream);
-    if (e != cudaSuccess) return (int)e;
+    const MapSet *maps = tma ? tensor_maps(a.ori, a.cmp, a.cmpStride, RATIO == 128) : nullptr;
+    if (maps == nullptr) tma = false;
+    const CUtensorMap &ori_map = tma ? maps->ori_map : no_map, &cmp_map = tma ? maps->cmp_map : no_map,
+                      &cmp_page_map = tma ? maps->cmp_page_map : no_map;
     SharedKVDebug d = {};
     if (debug) {
         d = *debug;
@@ -1472,21 +1464,15 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
 
 }  // namespace
 
-#ifdef SHAREDKV_TIMING
-extern "C" __attribute__((visibility("default"))) int sharedkv_timing_read(unsigned long long *host, int reset)
+int workspace_status(const void *workspace, cudaStream_t stream)
 {
-    cudaError_t e = cudaMemcpyFromSymbol(host, g_wait_cycles, sizeof(g_wait_cycles));
-    if (e == cudaSuccess && reset) {
-        static unsigned long long zeros[kMaxCtas][450];
-        e = cudaMemcpyToSymbol(g_wait_cycles, zeros, sizeof(zeros));
-    }
-    return (int)e;
-}
-#endif
-
-uint64_t workspace_bytes(uint32_t tokens)
-{
-    return ws_partials(tokens) + (uint64_t)kMaxCtas * 2ull * kPartialFloats * 4ull;
+    if (workspace == nullptr) return SHAREDKV_EINVAL;
+    uint32_t status = 0;
+    cudaError_t e = cudaMemcpyAsync(&status, static_cast<const char *>(workspace) + kWsStatus, sizeof(status),
+                                    cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return (int)e;
+    return status == kStatusOk ? SHAREDKV_OK : SHAREDKV_ETIMEDOUT;
 }
 
 int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, const SharedKVDebug *debug)

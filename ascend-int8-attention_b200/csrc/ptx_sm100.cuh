@@ -35,20 +35,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return done != 0;
 }
-// Non-blocking probe of a phase (try_wait may suspend the thread for a while when the phase is
-// still open; a thread that polls several barriers must not).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
 // One arrival that also announces `bytes` of asynchronous (TMA) traffic to the current phase.
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
 {
@@ -57,6 +43,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void fence_mbar_init()
 {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while its
+// predecessor in the stream is still running.  wait: blocks until the predecessor has completed and
+// its memory operations are visible (returns at once for a normal launch).  launch_dependents: lets
+// the successor's CTAs be scheduled as soon as every CTA of this grid has said so or exited.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- cp.async (16-byte, L2 only)

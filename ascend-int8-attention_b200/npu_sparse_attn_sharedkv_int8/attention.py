@@ -108,6 +108,11 @@ class PreparedAttention:
         self.query_group, self.tile_size, self.splits = 1, 128, 1
         self.adaptive_splits = self.trim_cube_tails = self.dynamic_grouped_c128 = False
         self.dynamic_c4, self.dynamic_c128 = case.ratio == 4, case.ratio == 128
+        _require(max_seq_len is None or (isinstance(max_seq_len, int) and max_seq_len > 0
+                                         and max_seq_len <= case.ori_block_table.shape[1] * case.ori.shape[1]
+                                         and (case.ratio == 1 or max_seq_len // case.ratio
+                                              <= case.cmp_block_table.shape[1] * case.cmp.shape[1])),
+                 "max_seq_len exceeds what the block tables can address")
         self.max_seq_len = max_seq_len
         self.workspace = self.partial = None
         self.blocks = 0

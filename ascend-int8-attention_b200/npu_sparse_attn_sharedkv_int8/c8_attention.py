@@ -100,6 +100,11 @@ def prepare(entry, *, scratch_allocator=None, shared_storage=False):
                      else torch.empty(need, dtype=torch.uint8, device=device))
     if workspace.data_ptr() % 256:
         raise ValueError("Attention workspace must be 256-byte aligned")
+    # Split-K arrival counters and the status word at the head of the workspace start at zero; the
+    # kernels keep them so from launch to launch, so this is the only clear a workspace ever gets
+    # (stream-ordered, on the current stream, like every launch that will use it).
+    with torch.cuda.device(device):
+        check(library().sharedkv_workspace_init(workspace.data_ptr(), current_stream(device.index)), "workspace init")
     partial = getattr(entry, "partial", None)
     if partial is None:
         partial = torch.empty(0, dtype=torch.float32, device=device)       # kept for callers that read `.partial`
@@ -134,6 +139,14 @@ def native_host(queued=False):
         return None
     call = module.attention_queued if queued else module.attention
     return SimpleNamespace(attention=call, attention_args_size=module.attention_args_size, _owner=module)
+
+
+def workspace_status(entry):
+    """Synchronises the current stream and raises RuntimeError if a wait inside a decode kernel that
+    used this entry's workspace ever ran out (its outputs are then invalid).  Diagnostic only."""
+    with torch.cuda.device(entry.case.q.device):
+        check(library().sharedkv_workspace_status(entry.workspace.data_ptr(), current_stream(entry.device_index)),
+              "attention kernel")
 
 
 def launch_raw(entry):

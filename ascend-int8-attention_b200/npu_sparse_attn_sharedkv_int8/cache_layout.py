@@ -49,12 +49,14 @@ def _round_up(value, multiple):
 
 
 def uses_compact(groups):
-    """True when any layer is an INT8 D=512 shared-KV cache (cache_layout.py:24-29)."""
+    """True when any layer is an INT8 D=512 shared-KV cache of a DeepSeek-V4 model
+    (cache_layout.py:24-29): the three conditions of the reference, `model_version` included."""
     for group in groups:
         if group is None or getattr(group, "kv_cache_spec", None) is None:
             continue
         for spec in _specs_of(group).values():
-            if spec.dtype == torch.int8 and getattr(spec, "head_size", None) == 512:
+            if (spec.dtype == torch.int8 and getattr(spec, "head_size", None) == 512
+                    and getattr(spec, "model_version", None) == "deepseek_v4"):
                 return True
     return False
 

@@ -41,6 +41,11 @@ def _library():
     lib.sharedkv_attention_debug.argtypes = [u32, ptr, ptr, ptr]
     lib.sharedkv_attention_debug.restype = ctypes.c_int
     lib.sharedkv_status_string.argtypes, lib.sharedkv_status_string.restype = [ctypes.c_int], ctypes.c_char_p
+    lib.sharedkv_workspace_init.argtypes, lib.sharedkv_workspace_init.restype = [ptr, ptr], ctypes.c_int
+    lib.sharedkv_workspace_status.argtypes, lib.sharedkv_workspace_status.restype = [ptr, ptr], ctypes.c_int
+    lib.sharedkv_attention_static_scratch.argtypes = [u32, ptr, ptr]
+    lib.sharedkv_attention_static_scratch.restype = ctypes.c_int
+    lib.sharedkv_static_scratch_status.argtypes, lib.sharedkv_static_scratch_status.restype = [ptr], ctypes.c_int
     return lib
 
 

@@ -212,21 +212,29 @@ def runtime(impl):
     return state
 
 
-def install(attention_impl=None, cache_layers=()):
+def install(attention_impl=None, cache_layers=(), *, planner=None, runner=None):
     """Route a serving stack's D=512 sparse shared-KV layers through this package.
 
     The reference patches vllm-ascend's DSA classes in place (vllm_adapter.py:225-277).  CUDA vLLM
     ships no such layer, so the classes to patch are passed in: `attention_impl` needs
     `get_kv_plan()` returning a dataclass with a `sparse_attn_op` field and a
     `_write_kv_cache(cache, kv, slot_mapping, *, quantize)` method; every class in `cache_layers`
-    needs `get_kv_cache_spec(config)` returning a dataclass with `head_size` and `dtype`.
+    needs `get_kv_cache_spec(config)` returning a dataclass with `head_size`, `dtype` and (where
+    the stack pads pages) `page_size_padded`.  SHAREDKV_COMPACT_PAGES=1 also installs the compact
+    page planner (cache_layout.install), which needs the stack's `planner` and `runner` objects;
+    without compact pages an INT8 layer keeps the BF16 pool's page size as padding, as in the
+    reference (vllm_adapter.py:258-262).
     """
-    from dataclasses import replace
+    from dataclasses import fields, replace
     load_scales()            # fail before weight loading if the calibration file is absent
     if attention_impl is None:
         raise RuntimeError("No CUDA serving stack exposes the sparse shared-KV layer hooks this adapter patches; "
                            "pass the implementation class to install(attention_impl=..., cache_layers=...) "
                            "or use LayerRuntime directly")
+    compact_pages = os.environ.get("SHAREDKV_COMPACT_PAGES") == "1"
+    if compact_pages:
+        from .cache_layout import install as install_cache_layout
+        install_cache_layout(planner, runner)
     original_plan = attention_impl.get_kv_plan
 
     def get_plan(self):
@@ -249,6 +257,9 @@ def install(attention_impl=None, cache_layers=()):
                 return None
             if old.head_size != 512 or old.dtype != torch.bfloat16:
                 raise ValueError("INT8 plugin expects the ordinary BF16 D=512 cache specification")
-            return replace(old, dtype=torch.int8)
+            changes = {"dtype": torch.int8}
+            if any(f.name == "page_size_padded" for f in fields(old)):
+                changes["page_size_padded"] = None if compact_pages else old.page_size_bytes
+            return replace(old, **changes)
 
         cls.get_kv_cache_spec = spec

@@ -19,9 +19,17 @@
  * Rules of the boundary
  *   - plain C types only; every pointer field is a device address of the GPU
  *     that is current (or named by `device`) when the call is made;
- *   - the library allocates nothing, synchronises nothing and reads nothing
- *     back: all scratch comes in through SharedKVArgs.workspace, whose size the
- *     caller obtains from sharedkv_workspace_bytes();
+ *   - the library allocates nothing, and its launch entries synchronise nothing
+ *     and read nothing back: all scratch comes in through SharedKVArgs.workspace,
+ *     whose size the caller obtains from sharedkv_workspace_bytes() and whose first
+ *     SHAREDKV_WORKSPACE_INIT_BYTES bytes the caller zeroes once, before the first
+ *     launch that uses it (sharedkv_workspace_init); every launch leaves them as
+ *     the next one needs them, so no memset runs in front of a kernel;
+ *   - a launch is one kernel.  It is launched with the programmatic-stream-
+ *     serialization attribute, i.e. its thread blocks may become resident while
+ *     the preceding kernel of the stream drains; they touch no global memory
+ *     before that kernel has completed (SHAREDKV_PDL=0 in the environment turns
+ *     the attribute off);
  *   - argument structs are copied by value at launch, so the caller may rebind
  *     or free the host struct as soon as the call returns;
  *   - launches go to the stream handed in (a cudaStream_t passed as void*) and
@@ -63,7 +71,8 @@ typedef struct SharedKVArgs {
     uint64_t seqLens;    /* INT32 [batch] KV length including the query tokens       */
     uint64_t sinks;      /* FP32 [heads] sink logits                                 */
     uint64_t out;        /* BF16 [tokens, heads, 512]                                */
-    uint64_t workspace;  /* >= sharedkv_workspace_bytes(tokens) bytes, 256-aligned   */
+    uint64_t workspace;  /* >= sharedkv_workspace_bytes(tokens) bytes, 256-aligned,
+                            first 1024 bytes zeroed once by the owner              */
     uint64_t lse;        /* FP32 [tokens, heads] or 0                                */
     uint64_t oriStride;  /* bytes between original pages (>= oriBlock * 512)         */
     uint64_t cmpStride;  /* bytes between compressed pages                           */
@@ -87,7 +96,8 @@ enum {
     SHAREDKV_OK = 0,
     SHAREDKV_EINVAL = -22,     /* null pointer, unsupported geometry, bad alignment  */
     SHAREDKV_ERANGE = -34,     /* batch / tokens beyond what the workspace can plan   */
-    SHAREDKV_EVARIANT = -2     /* unknown kernel variant (launch.cpp:45 throws there) */
+    SHAREDKV_EVARIANT = -2,    /* unknown kernel variant (launch.cpp:45 throws there) */
+    SHAREDKV_ETIMEDOUT = -110  /* sharedkv_workspace_status: a device-side wait ran out */
 };
 
 /* Kernel variants of the host bridge (c8_launch.cpp:12-18). */
@@ -105,6 +115,25 @@ SHAREDKV_API uint32_t sharedkv_attention_variant_count(void);
  * Replaces the Python-side constant c8_attention.WORKSPACE_BYTES
  * (npu_sparse_attn_sharedkv_int8/c8_attention.py:22-30). */
 SHAREDKV_API uint64_t sharedkv_workspace_bytes(uint32_t tokens);
+
+/* Prepares a freshly allocated (or otherwise overwritten) workspace: clears its first
+ * SHAREDKV_WORKSPACE_INIT_BYTES bytes (split-K arrival counters and the status word) with a
+ * memset on `stream`.  Needed once per workspace, not per launch: the kernel that finishes a
+ * split token puts the token's counter back to zero.  A workspace may be shared by launches of
+ * different shapes on one stream (the serving scratch pool of the reference,
+ * npu_sparse_attn_sharedkv_int8/vllm_adapter.py:41-49): the cleared region does not depend on the
+ * token count.  The reference has no such call; its kernels use no cross-core counters. */
+#define SHAREDKV_WORKSPACE_INIT_BYTES 1024u
+SHAREDKV_API int sharedkv_workspace_init(void *workspace, void *stream);
+
+/* Failure report of the decode kernel.  Every wait inside the kernel (on a row fetch, a tensor-core
+ * product, another warp) is bounded; when one runs out, the thread block gives up, frees its
+ * tensor memory, and sets a status word in the workspace that stays set until the workspace is
+ * initialised again.  This call synchronises `stream`, reads the word and returns SHAREDKV_OK,
+ * SHAREDKV_ETIMEDOUT (the outputs of some launch that used this workspace are invalid) or a
+ * cudaError_t.  It is a diagnostic: nothing on the launch path calls it.  The reference reports
+ * device failures through its runtime's stream errors instead. */
+SHAREDKV_API int sharedkv_workspace_status(const void *workspace, void *stream);
 
 /* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
  * query token.  `blocks` is accepted for signature compatibility and ignored: the
@@ -138,9 +167,11 @@ SHAREDKV_API int sharedkv_cache_write(uint64_t args, uint32_t blocks, int32_t de
  *   pvAcc     INT32 [maxTiles, 512, 16] PV accumulators
  *   qCodes    INT8  [tokens, 2, 16, 512] query code planes per cache kind
  *   counter   UINT32 [1]                 tiles dumped (zeroed by the caller)
- * `reserved`: bits 0-30, when non-zero, cap the number of CTAs (1 = every token is processed as
+ * `reserved`: bits 0-15, when non-zero, cap the number of CTAs (1 = every token is processed as
  * one piece, like the reference's single running state); bit 31 selects the cp.async row
- * gather instead of the TMA gather.
+ * gather instead of the TMA gather; bit 30 lowers the kernel's wait limit to about a millisecond
+ * and lets one barrier arrival go missing, so that a test can watch the time-out path end the
+ * kernel and set the status word.
  * No counterpart in the reference; its oracle computes these inline
  * (npu_sparse_attn_sharedkv_int8/reference.py:287-289,310-313). */
 typedef struct SharedKVDebug {
@@ -168,13 +199,17 @@ SHAREDKV_API const char *sharedkv_status_string(int status);
  *   - The first call on each device looks the array's address up (with that device current, which
  *     is the caller's job as for every launch_* entry).  Make that first call outside any stream
  *     capture; later calls only launch kernels.
- *   - The array needs no clearing, before the first call or between calls: each call rebuilds
- *     what it reads.
+ *   - The array needs no clearing, before the first call or between calls: it is zero when the
+ *     library is loaded and every call leaves it as the next one needs it.
+ *   - The status word of a timed-out wait lives in the array too; read it with
+ *     sharedkv_static_scratch_status(stream), which synchronises `stream` and returns SHAREDKV_OK,
+ *     SHAREDKV_ETIMEDOUT or a cudaError_t.
  *   - All calls on a device share the array.  Calls on one stream are ordered and safe; calls that
  *     can overlap in time (different streams or threads) race on it and give wrong results.  Use
  *     the workspace-taking entries with one workspace per stream for those. */
 #define SHAREDKV_STATIC_SCRATCH_MAX_TOKENS 4096u
 SHAREDKV_API int sharedkv_attention_static_scratch(uint32_t variant, void *stream, const SharedKVArgs *args);
+SHAREDKV_API int sharedkv_static_scratch_status(void *stream);
 
 #ifdef __cplusplus
 }

@@ -98,10 +98,76 @@ def windowed_case(ref, *, ratio, queries, lengths, seed, topk=1024, edit_indices
     return case, oq, cq
 
 
+def layout_golden(reference):
+    """cache_layout.json: offsets, strides and group splits computed by the reference's own
+    `cache_layout.uses_compact / group_specs / packed_layout` (npu_sparse_attn_sharedkv_int8/
+    cache_layout.py:24-85) on vLLM's real cache-spec objects.  Only that one file of the reference is
+    loaded (by path: its package name is also this build's), and it imports nothing but vLLM."""
+    import importlib.util
+    import json
+    from vllm.v1.kv_cache_interface import KVCacheGroupSpec, MLAAttentionSpec, UniformTypeKVCacheSpecs
+    spec = importlib.util.spec_from_file_location('reference_cache_layout',
+                                                  reference / 'npu_sparse_attn_sharedkv_int8' / 'cache_layout.py')
+    layout = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(layout)
+
+    def mla(dtype, head_size, block_size=32, padded=None, ratio=1, version='deepseek_v4'):
+        return MLAAttentionSpec(block_size=block_size, num_kv_heads=1, head_size=head_size, dtype=dtype,
+                                page_size_padded=padded, compress_ratio=ratio, model_version=version)
+
+    def describe(name, s):
+        return dict(name=name, dtype=str(s.dtype).replace('torch.', ''), page_size_bytes=s.page_size_bytes,
+                    head_size=s.head_size, block_size=s.block_size, num_kv_heads=s.num_kv_heads,
+                    page_size_padded=s.page_size_padded, model_version=getattr(s, 'model_version', None),
+                    unpadded_page_size_bytes=replace(s, page_size_padded=None).page_size_bytes)
+
+    def uniform(specs):
+        merged = UniformTypeKVCacheSpecs.from_specs(specs)
+        assert merged is not None
+        return merged
+
+    scenarios = {}
+    # the serving geometry of the reference's device tests: 38 INT8 D=512 layers in one group
+    # (38 x 16 384 = 622 592 bytes per block) beside a group of FP32 compressor states
+    attention = {f'model.layers.{i}.attn': mla(torch.int8, 512) for i in range(38)}
+    states = {f'model.layers.{i}.state': mla(torch.float32, 130, block_size=8) for i in range(6)}
+    scenarios['serving38'] = [attention, states]
+    # vLLM's own page sizes for compressed layers (a page holds block_size / compress_ratio rows)
+    scenarios['compressed_pages'] = [{f'm.{i}.attn': mla(torch.int8, 512, ratio=4 if i % 2 == 0 else 128) for i in range(6)}]
+    # mixed sizes inside a group: ordering by size and alignment
+    scenarios['mixed'] = [{'a.small': mla(torch.int8, 100), 'a.big': mla(torch.int8, 512), 'a.mid': mla(torch.int8, 129)},
+                          {'b.f32': mla(torch.float32, 65), 'b.big': mla(torch.int8, 512)}]
+    # INT8 D=512 caches of another model version, and BF16 caches: not compact
+    scenarios['other_model'] = [{'x.attn': mla(torch.int8, 512, version='deepseek_v3')}]
+    scenarios['bf16'] = [{'y.attn': mla(torch.bfloat16, 512)}]
+    result = {}
+    for name, groups in scenarios.items():
+        group_objects = [KVCacheGroupSpec(list(specs), uniform(specs)) for specs in groups]
+        stride, offsets = layout.packed_layout(group_objects)
+        result[name] = dict(groups=[[describe(n, s) for n, s in specs.items()] for specs in groups],
+                            uses_compact=bool(layout.uses_compact(group_objects)), stride=stride, offsets=offsets,
+                            pool_bytes_per_block=layout.pool_bytes_per_block(group_objects))
+    # group_specs: C4 (cache + indexer), C128, and an over-full group of padded FP32 states
+    c4 = {'l0.c4': mla(torch.int8, 512, ratio=4), 'l0.indexer': mla(torch.int8, 132, ratio=4)}
+    c128 = {'l1.c128': mla(torch.int8, 512, ratio=128)}
+    padded = {f'l{i}.state': mla(torch.float32, 128, padded=32768) for i in range(5)}
+    grouped = [uniform(c4), uniform(c128), uniform(padded)]
+    split = layout.group_specs(grouped)
+    result['group_specs'] = dict(
+        groups=[[describe(n, s) for n, s in specs.items()] for specs in (c4, c128, padded)],
+        split=[[describe(n, g.kv_cache_spec.kv_cache_specs[n]) for n in g.layer_names] for g in split])
+    (HERE / 'cache_layout.json').write_text(json.dumps(result, indent=1, sort_keys=True) + '\n')
+    print('cache_layout', {k: v.get('stride') for k, v in result.items()}, flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument('--reference', type=Path, required=True, help='checkout of the reference project')
+    parser.add_argument('--only-layout', action='store_true', help='regenerate cache_layout.json alone (needs vllm)')
     args = parser.parse_args()
+    if args.only_layout:
+        layout_golden(args.reference)
+        return
     sys.path.insert(0, str(args.reference))
     from npu_sparse_attn_sharedkv_int8 import reference as ref
     from tests.support.serving_shapes import ActivationCorpus, Geometry
@@ -174,6 +240,8 @@ def main():
                        ori_block_table=source.ori_block_table[:, :math.ceil(max(lengths) / 32)].contiguous(),
                        cmp_block_table=source.cmp_block_table[:, :max(1, math.ceil(max(lengths) / (ratio * 32)))].contiguous())
         save_case(f'real_c{ratio}', case, oq, cq, ref)
+
+    layout_golden(args.reference)
 
 
 if __name__ == '__main__':

@@ -166,3 +166,21 @@ def test_two_ranks_shard_requests_and_combine_timings():
     assert counts[0] == 256 and counts[1] == results[0][3] + results[1][3]
     costs = [results[0][3], results[1][3]]
     assert max(costs) / min(costs) < 1.02
+
+
+def test_work_split_invariants_on_the_host(tmp_path):
+    """The device planner's arithmetic (csrc/work_split.h) compiled for the host and checked over
+    22 000 random workloads: every tile of every live token in exactly one item, unique workspace
+    entries below tokens + 160, no colliding partial-state slots or tickets, nobody beyond its quota
+    (reference precedent: tests/cpp/test_schedule.cpp:35-107)."""
+    import shutil
+    import subprocess
+    compiler = shutil.which("g++")
+    if compiler is None:
+        pytest.skip("no host C++ compiler")
+    binary = tmp_path / "test_work_split"
+    subprocess.run([compiler, "-std=c++17", "-O2", "-I", str(ROOT / "ascend-int8-attention_b200" / "csrc"),
+                    str(ROOT / "tests" / "cpp" / "test_work_split.cpp"), "-o", str(binary)], check=True)
+    done = subprocess.run([str(binary), "22000"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert "work split ok: 22000 workloads" in done.stdout

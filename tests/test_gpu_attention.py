@@ -53,7 +53,7 @@ def check_against_reference(out, lse, z, case=None, scales=None, ctas=None):
 def test_golden_cases(name):
     case, ori_scale, cmp_scale, z = load_case(name)
     op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
-    op.workspace.fill_(0xA5)
+    op.workspace[1024:].fill_(0xA5)                      # only the head of a workspace (cleared once, at prepare) has to be clean
     out = op.run()
     torch.cuda.synchronize()
     check_against_reference(out.cpu(), op.lse.cpu(), z, case, (ori_scale, cmp_scale))
@@ -153,6 +153,50 @@ def test_integer_stages_are_exact(name, ctas, legacy_gather):
     assert seen == set(by_key)
     if ctas == 1:
         assert p_differs <= max(2, p_total // 200), (p_differs, p_total)
+
+
+@pytest.mark.parametrize("name", ATTENTION_CASES)
+def test_production_kernel_gives_the_bits_of_the_instrumented_kernel(name):
+    """The integer-stage proofs above run the kernel instantiation that dumps its intermediates;
+    the instantiation that serving and the benchmark launch is another binary.  Same grid, same
+    work split, same arithmetic: its output and LSE must be the same bits."""
+    case, ori_scale, cmp_scale, _ = load_case(name)
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
+    out, lse = op.run().clone(), op.lse.clone()
+    torch.cuda.synchronize()
+    op.out.fill_(9.0)
+    op.lse.fill_(9.0)
+    run_debug(op, max_tiles=256)
+    assert torch.equal(op.out, out) and torch.equal(op.lse, lse)
+
+
+def test_a_wait_that_runs_out_ends_the_kernel_and_sets_the_status_word():
+    """Every wait inside the kernel is bounded.  The test entry can make one barrier arrival go
+    missing under a wait limit of about a millisecond: the warp that waits for it gives up, all
+    roles return, the CTA frees its tensor memory, the kernel ends, and the workspace's status word
+    says so until the workspace is initialised again.  Nothing hangs and the context stays usable:
+    the next ordinary launch is correct."""
+    from npu_sparse_attn_sharedkv_int8 import c8_attention, runtime
+    case, ori_scale, cmp_scale, z = load_case("unit_c4")
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
+    lib = runtime._library()
+    stream = runtime.current_stream(0)
+    assert lib.sharedkv_workspace_status(op.workspace.data_ptr(), stream) == 0
+    run_debug(op, max_tiles=64, ctas=1 | 0x40000000)
+    assert lib.sharedkv_workspace_status(op.workspace.data_ptr(), stream) == -110
+    with pytest.raises(RuntimeError, match="ran out"):
+        c8_attention.workspace_status(op)
+    # sticky: an ordinary launch does not clear it ...
+    out = op.run()
+    torch.cuda.synchronize()
+    check_against_reference(out.cpu(), op.lse.cpu(), z, case, (ori_scale, cmp_scale))
+    assert lib.sharedkv_workspace_status(op.workspace.data_ptr(), stream) == -110
+    # ... initialising the workspace does
+    assert lib.sharedkv_workspace_init(op.workspace.data_ptr(), stream) == 0
+    out = op.run()
+    torch.cuda.synchronize()
+    check_against_reference(out.cpu(), op.lse.cpu(), z, case, (ori_scale, cmp_scale))
+    assert lib.sharedkv_workspace_status(op.workspace.data_ptr(), stream) == 0
 
 
 def test_rebind_and_streams():

@@ -20,6 +20,7 @@ class Spec:
     scale_dtype: torch.dtype = torch.float32
     page_size_padded: int | None = None
     pages: int = 10
+    model_version: str | None = "deepseek_v4"
 
     def max_memory_usage_pages(self, config):
         return self.pages
@@ -50,6 +51,63 @@ def test_packed_layout_gives_the_reference_serving_stride():
     assert states == [4160 * i for i in range(4)] and all(v % 4 == 0 for v in states)
     assert cache_layout.uses_compact(groups) and not cache_layout.uses_compact([groups[1]])
     assert cache_layout.max_memory_usage(None, groups) == stride * 20
+
+
+def test_layout_matches_the_reference_planner_on_vllm_specs():
+    """tests/golden/cache_layout.json holds what the reference's own uses_compact / packed_layout /
+    group_specs (cache_layout.py:24-85 of the reference) returned for vLLM's real cache-spec
+    objects; the same numbers fed to this build's duck-typed planner must give the same strides,
+    offsets, compact decision and group split."""
+    import json
+    from pathlib import Path
+    golden = json.loads((Path(__file__).resolve().parent / "golden" / "cache_layout.json").read_text())
+
+    def spec_of(d):
+        return Spec(getattr(torch, d["dtype"]), d["page_size_bytes"], head_size=d["head_size"],
+                    num_kv_heads=d["num_kv_heads"], block_size=d["block_size"], page_size_padded=d["page_size_padded"],
+                    model_version=d["model_version"])
+
+    checked = 0
+    for name, want in golden.items():
+        if name == "group_specs":
+            continue
+        groups = [group({d["name"]: spec_of(d) for d in layers}) for layers in want["groups"]]
+        stride, offsets = cache_layout.packed_layout(groups)
+        assert stride == want["stride"] == cache_layout.pool_bytes_per_block(groups), name
+        assert offsets == want["offsets"], name
+        assert cache_layout.uses_compact(groups) == want["uses_compact"], name
+        checked += 1
+    assert checked >= 5 and golden["serving38"]["stride"] == 622592
+    @dataclass(frozen=True)
+    class PageSpec:
+        """As vLLM's specs: the page size follows from the geometry unless a padded size is set."""
+        dtype: torch.dtype
+        head_size: int
+        unpadded: int
+        page_size_padded: int | None
+        model_version: str | None
+
+        @property
+        def page_size_bytes(self):
+            return self.unpadded if self.page_size_padded is None else self.page_size_padded
+
+    def page_spec_of(d):
+        made = PageSpec(getattr(torch, d["dtype"]), d["head_size"], d["unpadded_page_size_bytes"],
+                        d["page_size_padded"], d["model_version"])
+        assert made.page_size_bytes == d["page_size_bytes"]
+        return made
+
+    want = golden["group_specs"]
+    inputs = []
+    for layers in want["groups"]:
+        specs = {d["name"]: page_spec_of(d) for d in layers}
+        inputs.append(SimpleNamespace(kv_cache_specs=specs, page_size_bytes=sum(s.page_size_bytes for s in specs.values())))
+    out = cache_layout.group_specs(inputs)
+    assert [names for names, _ in out] == [[d["name"] for d in g] for g in want["split"]]
+    for (names, specs), g in zip(out, want["split"]):
+        for d in g:
+            assert specs[d["name"]].page_size_bytes == d["page_size_bytes"]
+            assert specs[d["name"]].page_size_padded == d["page_size_padded"]
 
 
 def test_layout_orders_by_size_aligns_scales_and_rejects_duplicates():

@@ -80,6 +80,50 @@ def test_alternating_layer_kinds_share_the_array():
         assert torch.equal(out, wanted[k])
 
 
+@pytest.mark.parametrize("ratio", (4, 128))
+def test_the_largest_accepted_call(ratio):
+    """As many query rows as the entry accepts (the item list and the partial states then reach the
+    top of their areas in the array), many of them split over several CTAs: same bits as the
+    workspace-taking launch, twice in a row; the array's status word stays clear."""
+    from types import SimpleNamespace
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    from npu_sparse_attn_sharedkv_int8.reference import SharedKVCase
+    runtime, static_scratch = entry()
+    tokens, pages = max_tokens(), 512
+    g = torch.Generator().manual_seed(99 + ratio)
+    queries = torch.randint(1, 4, (tokens,), generator=g)
+    cu = torch.cat((torch.zeros(1, dtype=torch.int64), torch.cumsum(queries, 0)))
+    batch = int((cu <= tokens).sum()) - 1
+    cu = cu[:batch + 1].clone()
+    cu[-1] = tokens                                         # the last request takes what is left
+    lengths = torch.randint(200, 9000, (batch,), generator=g, dtype=torch.int32)
+    lengths = torch.maximum(lengths, (cu[1:] - cu[:-1]).to(torch.int32))
+    case = SharedKVCase(
+        q=torch.randn(tokens, 8, 512, generator=g).bfloat16(),
+        ori=torch.randint(-127, 128, (pages, 32, 1, 512), generator=g, dtype=torch.int8),
+        ori_block_table=torch.randint(0, pages, (batch, 282), generator=g, dtype=torch.int32),
+        cu_q=cu.to(torch.int32), seq_lens=lengths, sink=torch.linspace(-2, 2, 8),
+        cmp=torch.randint(-127, 128, (pages, 32, 1, 512), generator=g, dtype=torch.int8),
+        cmp_block_table=torch.randint(0, pages, (batch, 71), generator=g, dtype=torch.int32),
+        cmp_indices=torch.randint(-1, 2300, (tokens, 1, 1024), generator=g, dtype=torch.int32) if ratio == 4 else None,
+        ratio=ratio)
+    scale = (torch.rand(512, generator=g) * 0.02 + 0.005).to(DEVICE)
+    op = PreparedAttention(case.to(DEVICE), scale, scale, return_lse=True)
+    expected, expected_lse = op.run().clone(), op.lse.clone()
+    torch.cuda.synchronize()
+    out, lse = torch.empty_like(expected), torch.empty_like(expected_lse)
+    args = type(op.args).from_buffer_copy(op.args)
+    args.out, args.lse, args.workspace = out.data_ptr(), lse.data_ptr(), 0
+    assert args.tokens == tokens
+    for call in range(2):
+        out.fill_(7.0)
+        lse.fill_(7.0)
+        runtime.check(static_scratch(op.variant, runtime.current_stream(0), ctypes.byref(args)), "static-scratch launch")
+        torch.cuda.synchronize()
+        assert torch.equal(out, expected) and torch.equal(lse, expected_lse), call
+    assert runtime._library().sharedkv_static_scratch_status(runtime.current_stream(0)) == 0
+
+
 def test_more_rows_than_the_limit_are_refused():
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
     runtime, static_scratch = entry()
@@ -92,4 +136,5 @@ def test_more_rows_than_the_limit_are_refused():
     with pytest.raises(RuntimeError, match="beyond"):
         runtime.check(status, "static-scratch launch")
     assert static_scratch(op.variant, runtime.current_stream(0), None) == -22
+    assert static_scratch(99, runtime.current_stream(0), ctypes.byref(args)) == -2       # the variant is checked first
     torch.cuda.synchronize()
