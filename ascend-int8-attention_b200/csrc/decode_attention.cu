@@ -110,7 +110,8 @@ constexpr uint32_t kBarFull = 0, kBarEmpty = 3, kBarSFull = 6, kBarSFree = 8, kB
                    kBarGroup = 22 /* x4: softmax halves, all softmax, all accumulate */,
                    kBarRescale = 26 /* x8 */, kBarItemDone = 34 /* x8 */, kNumBars = 42;
 constexpr uint32_t kSmMisc = kSmBar + kNumBars * 8;          // tmem base, abort flag, two broadcast words, wait limit
-constexpr uint32_t kSmemBytes = kSmMisc + 32 + 1024;         // + alignment slack
+constexpr uint32_t kSmPlan = kSmMisc + 32;                   // PlanResult: this CTA's share of the launch (48 bytes)
+constexpr uint32_t kSmemBytes = kSmPlan + 48 + 1024;         // + alignment slack
 static_assert(kSmemBytes <= 232448, "dynamic shared memory limit of sm_100");
 
 // tensor-memory columns
@@ -181,15 +182,18 @@ __device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_ba
 // of the flat tile list become its items, written to workspace entries no other CTA uses.
 // `scratch` is shared memory the roles do not use yet (the KV ring).
 struct PlanResult {
-    uint32_t first, end, live_tokens;
+    uint32_t first, end, live_tokens, tiles;      // this CTA's entries [first, end) and the tiles they hold
+    uint4 first_lo, first_hi;                     // its first item, so that no role starts with a global read
 };
 struct PlanScratch {
     uint32_t scan[80];
-    uint32_t live, mismatch, first, count;
+    uint32_t live, mismatch, first, count, head, tail, tiles, pad;
+    uint4 first_item[2];
     int32_t cu[kPlanStaged];
 };
+static_assert(sizeof(PlanResult) == 48, "PlanResult has its own 48 bytes of shared memory");
 template <int RATIO>
-__device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch *sc)
+__device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch *sc, PlanResult *result)
 {
     const uint32_t tid = threadIdx.x;
     const int32_t *cu_global = reinterpret_cast<const int32_t *>(p.cuQ);
@@ -197,7 +201,9 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     char *ws = reinterpret_cast<char *>(p.workspace);
     Item *items = reinterpret_cast<Item *>(ws + kWsItems);
 
-    if (tid == 0) { sc->live = 0; sc->mismatch = 0xffffffffu; sc->first = 0xffffffffu; sc->count = 0; }
+    if (tid == 0) {
+        sc->live = 0; sc->mismatch = 0xffffffffu; sc->first = 0xffffffffu; sc->count = 0; sc->head = 0; sc->tail = 0; sc->tiles = 0;
+    }
     const bool staged = p.batch + 1u <= kPlanStaged;
     const int32_t seq_first = tid < p.batch ? seq[tid] : 0;      // in flight together with the cuQ reads
     if (staged)
@@ -236,40 +242,74 @@ __device__ PlanResult plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanS
     const uint32_t quota = split::quota_of(split::total_cost(total_tiles, live_tokens), grid);
     const uint32_t me = blockIdx.x;
 
-    // Only threads whose tokens overlap this CTA's range [me * quota, (me + 1) * quota) go on.
+    // Only threads whose tokens overlap this CTA's range [me * quota, (me + 1) * quota) go on.  Two
+    // rounds over their tokens: the first finds where the CTA's entries begin, how many there are and
+    // whether the range begins / ends inside a token; the second writes the items.
+    //
+    // Order of a CTA's items.  A range that ends inside a token holds that token's first piece, and
+    // the CTA after it holds the next piece at the very front of its range.  Walked in token order
+    // the first piece would be the last thing this CTA does, and the split-K merge (partial state to
+    // global memory, ticket, the other pieces read back) would sit at the end of every CTA's
+    // critical path.  So that piece is moved up: a piece continued from the previous CTA first (it
+    // is the one the previous CTA is waiting for), then the piece continuing into the next CTA,
+    // then the whole tokens.  Both ends of a split token are then finished early in the kernel and
+    // the merge overlaps the tiles that follow.
     const uint32_t range_begin = split::first_tile_position(tile_base, t_begin) - split::kItemCost;
     const uint32_t range_end = split::first_tile_position(tile_base + my_tiles, t_end) - split::kItemCost;
-    if (range_begin < (me + 1) * quota && range_end > me * quota) {
-        uint32_t before = tile_base;
-        for (uint32_t t = t_begin; t < t_end; ++t) {
-            uint32_t batch; int32_t position;
-            const uint32_t n = tiles_of(t, batch, position);
-            const uint32_t start = split::first_tile_position(before, t);
-            const split::Pieces pc = split::pieces_of(start, n, quota);
-            if (me >= pc.first_cta && me < pc.first_cta + pc.count) {
-                const split::TileRange r = split::piece_range(start, n, quota, me);
-                const uint32_t entry = split::item_index(t, me);
-                uint4 *dst = reinterpret_cast<uint4 *>(items + entry);
-                dst[0] = make_uint4(t, batch, (uint32_t)position, r.begin);
-                dst[1] = make_uint4(r.end, me - pc.first_cta, pc.count, pc.first_cta);
-                atomicMin(&sc->first, entry);
-                atomicAdd(&sc->count, 1u);
+    const bool overlaps = range_begin < (me + 1) * quota && range_end > me * quota;
+#pragma unroll 1
+    for (int round = 0; round < 2; ++round) {
+        const uint32_t first = sc->first, count = sc->count;        // round 1: complete (read behind the barrier below)
+        const uint32_t head = sc->head ? 1u : 0u;
+        const bool rotate = round == 1 && sc->tail && count > head + 1u;
+        if (overlaps) {
+            uint32_t before = tile_base;
+            for (uint32_t t = t_begin; t < t_end; ++t) {
+                uint32_t batch; int32_t position;
+                const uint32_t n = tiles_of(t, batch, position);
+                const uint32_t start = split::first_tile_position(before, t);
+                const split::Pieces pc = split::pieces_of(start, n, quota);
+                if (me >= pc.first_cta && me < pc.first_cta + pc.count) {
+                    const uint32_t entry = split::item_index(t, me), part = me - pc.first_cta;
+                    if (round == 0) {
+                        atomicMin(&sc->first, entry);
+                        atomicAdd(&sc->count, 1u);
+                        if (part > 0) sc->head = 1u;                                  // continued from the previous CTA
+                        if (part + 1u < pc.count) sc->tail = 1u;                      // continues into the next CTA
+                    } else {
+                        uint32_t place = entry - first;                               // position in token order
+                        if (rotate) place = split::rotated_place(place, count, head);
+                        const split::TileRange r = split::piece_range(start, n, quota, me);
+                        uint4 *dst = reinterpret_cast<uint4 *>(items + first + place);
+                        const uint4 lo = make_uint4(t, batch, (uint32_t)position, r.begin);
+                        const uint4 hi = make_uint4(r.end, part, pc.count, pc.first_cta);
+                        dst[0] = lo;
+                        dst[1] = hi;
+                        if (place == 0) { sc->first_item[0] = lo; sc->first_item[1] = hi; }
+                        atomicAdd(&sc->tiles, r.end - r.begin);
+                    }
+                }
+                before += n;
             }
-            before += n;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        PlanResult r;
+        r.first = sc->count ? sc->first : 0u;
+        r.end = r.first + sc->count;
+        r.live_tokens = live_tokens;
+        r.tiles = sc->tiles;
+        r.first_lo = sc->first_item[0];
+        r.first_hi = sc->first_item[1];
+        *result = r;
+        if (me == 0) {
+            PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
+            header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
+            header->quota = quota; header->n_items = live_tokens; header->grid = grid;
         }
     }
-    __syncthreads();
-    PlanResult r;
-    r.first = sc->count ? sc->first : 0u;
-    r.end = r.first + sc->count;
-    r.live_tokens = live_tokens;
-    if (me == 0 && tid == 0) {
-        PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
-        header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
-        header->quota = quota; header->n_items = live_tokens; header->grid = grid;
-    }
-    __syncthreads();          // the scratch area is handed back to the KV ring
-    return r;
+    __syncthreads();          // the result is published and the scratch area is handed back to the KV ring
 }
 // ------------------------------------------------------------------ decode kernel pieces
 struct Shared {
@@ -335,11 +375,6 @@ __device__ __forceinline__ Item decode_item(const uint4 &a, const uint4 &b)
     it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
     return it;
 }
-__device__ __forceinline__ Item load_item(const Item *items, uint32_t index)
-{
-    const uint4 *src = reinterpret_cast<const uint4 *>(items + index);
-    return decode_item(src[0], src[1]);
-}
 __device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items)
 {
     if (c.item + 1 < c.items_end) {
@@ -348,12 +383,12 @@ __device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items)
         c.next_hi = src[1];
     }
 }
-__device__ __forceinline__ void cursor_init(Cursor &c, const Item *items, uint32_t first, uint32_t end)
+__device__ __forceinline__ void cursor_init(Cursor &c, const Item *items, const PlanResult &plan)
 {
-    c.item = first; c.items_end = end; c.done = first >= end; c.j = 0;
+    c.item = plan.first; c.items_end = plan.end; c.done = plan.first >= plan.end; c.j = 0;
     c.next_lo = c.next_hi = make_uint4(0, 0, 0, 0);
     if (!c.done) {
-        c.it = load_item(items, first);
+        c.it = decode_item(plan.first_lo, plan.first_hi);
         c.j = c.it.tile_begin;
         cursor_prefetch(c, items);
     }
@@ -514,13 +549,14 @@ constexpr int kLookahead = 1;
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
 template <int RATIO, bool TMA>
-__device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, uint32_t first, uint32_t end,
+__device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan,
                               uint32_t set, uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
                               const CUtensorMap *cmp_page_map)
 {
     // set 0 fetches tiles 0, 2, 4 ... of the CTA, set 1 tiles 1, 3, 5 ...
+    const uint32_t first = plan.first, end = plan.end;
     Cursor ca;
-    cursor_init(ca, items, first, end);
+    cursor_init(ca, items, plan);
     if (!ca.done) ring_put(sm, set, ca.item, ca.it);
     if (set) leader_advance(ca, items, sm, set, 1);
     Follower cb, cc;
@@ -669,14 +705,14 @@ drain:
 // retires one per ~40, so the two products of a tile are issued by two threads of different
 // warps (different SM sub-partitions): S = K.Q^T by one, O = K^T.P by the other.  Each product is
 // 16 instructions of M = 128, N = 16, K = 32 bytes.
-__device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+__device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
     const bool leader = elect_one();
-    first = __shfl_sync(0xffffffffu, first, 0);        // loop bounds the compiler can see are the same in all lanes
-    end = __shfl_sync(0xffffffffu, end, 0);
+    const uint32_t first = __shfl_sync(0xffffffffu, plan.first, 0);        // loop bounds the compiler can see are the same in all lanes
+    const uint32_t end = __shfl_sync(0xffffffffu, plan.end, 0);
     Cursor cq;
-    cursor_init(cq, items, first, end);
+    cursor_init(cq, items, plan);
     uint32_t t = 0;                        // tiles issued so far
     for (uint32_t k = 0; k < end - first; ++k) {
         // Query codes: one buffer for the original kind (read by an item's first tile only) and two
@@ -728,17 +764,12 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, uint32_t first,
     }
 }
 
-__device__ void mma_pv_loop(const Shared &sm, const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+__device__ void mma_pv_loop(const Shared &sm, const PlanResult &plan, uint32_t tmem)
 {
     constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
     // only the number of tiles matters here
     const bool leader = elect_one();
-    uint32_t tiles = 0;
-    for (uint32_t k = first; k < end; ++k) {
-        const Item it = load_item(items, k);
-        tiles += it.tile_end - it.tile_begin;
-    }
-    tiles = __shfl_sync(0xffffffffu, tiles, 0);
+    const uint32_t tiles = __shfl_sync(0xffffffffu, plan.tiles, 0);
     for (uint32_t t = 0; t < tiles; ++t) {
         const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
         if (!wait_phase<3>(sm, kBarPReady + buf, ph)) return;
@@ -814,7 +845,7 @@ __device__ __forceinline__ float warp_reduce4(const float (&v)[4], uint32_t lane
 // per head.  Runs one item ahead of the S = K.Q^T issuer.
 template <bool DEBUG>
 __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
-                           uint32_t first, uint32_t end, uint32_t kind, uint32_t lane)
+                           const PlanResult &plan, uint32_t kind, uint32_t lane)
 {
     float sc[16];
     {
@@ -826,7 +857,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
         }
     }
     Cursor cur;
-    cursor_init(cur, items, first, end);
+    cursor_init(cur, items, plan);
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
         const bool used = kind == 0 ? it.tile_begin == 0 : it.tile_end > max(it.tile_begin, 1u);
@@ -912,7 +943,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
 
 template <int RATIO, bool DEBUG>
 __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
-                             uint32_t first, uint32_t end, uint32_t tmem)
+                             const PlanResult &plan, uint32_t tmem)
 {
     const uint32_t half = threadIdx.x >> 7;        // 0: heads 0-3, 1: heads 4-7
     const uint32_t key = threadIdx.x & 127u;       // key within a tile
@@ -927,7 +958,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
     for (int i = 0; i < 4; ++i) sink[i] = reinterpret_cast<const float *>(p.sinks)[half * 4u + i];
 
     Cursor cur;
-    cursor_init(cur, items, first, end);
+    cursor_init(cur, items, plan);
 
     uint32_t gt = 0;                               // tiles consumed so far by this CTA
     for (uint32_t k = 0; !cur.done; ++k) {
@@ -1065,7 +1096,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t x)
 
 template <int RATIO, bool DEBUG>
 __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const uint32_t live_tokens,
-                                const Item *items, uint32_t first, uint32_t end, uint32_t tmem)
+                                const Item *items, const PlanResult &plan, uint32_t tmem)
 {
     const uint32_t ch = threadIdx.x - 256u;        // 0..127
     const uint32_t warp = ch >> 5;
@@ -1096,7 +1127,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
     }
 
     Cursor cur;
-    cursor_init(cur, items, first, end);
+    cursor_init(cur, items, plan);
     uint32_t gt = 0;
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
@@ -1278,21 +1309,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
     // is read and written, which the previous kernel of the stream may still be producing or using
     // (a query projection, the cache writer, an attention launch that shares this workspace).
     grid_dependency_launch_dependents();
+    // The work split starts with cuQ and seqLens; ask for their lines now.  A prefetch consumes no
+    // value: whatever the previous kernel still writes there reaches L2 before the wait returns.
+    if (tid <= p.batch) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const int32_t *>(p.cuQ) + tid));
+        if (tid < p.batch) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const int32_t *>(p.seqLens) + tid));
+    }
     grid_dependency_wait();
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
-    const PlanResult plan = plan_cta<RATIO>(p, gridDim.x, reinterpret_cast<PlanScratch *>(sm.ptr + kSmKv));
-    const uint32_t first = plan.first, end = plan.end;
+    plan_cta<RATIO>(p, gridDim.x, reinterpret_cast<PlanScratch *>(sm.ptr + kSmKv), reinterpret_cast<PlanResult *>(sm.ptr + kSmPlan));
+    const PlanResult &plan = *reinterpret_cast<const PlanResult *>(sm.ptr + kSmPlan);
 
     // Roles by warpgroup (four warps, one per SM sub-partition); the register file is re-divided
     // first: the groups that need few registers release them before the others grow.
     if (warp < 8) {
         if (kRegsSoftmax > kRegsLaunch) registers_acquire<kRegsSoftmax>();
-        softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, first, end, tmem);
+        softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, plan, tmem);
     } else if (warp < kWarpProducer) {
         registers_acquire<kRegsAccumulate>();
-        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, plan.live_tokens, items, first, end, tmem);
+        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, plan.live_tokens, items, plan, tmem);
     } else if (warp < kWarpMma || warp >= kWarpProducerB) {
         registers_release<kRegsProducer>();
         if (TMA && lane == 0) {
@@ -1300,18 +1337,18 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
             tma_prefetch_descriptor(RATIO == 128 ? &cmp_page_map : &cmp_map);
         }
         const uint32_t set = warp >= kWarpProducerB ? 1u : 0u;
-        producer_loop<RATIO, TMA>(p, sm, items, first, end, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
+        producer_loop<RATIO, TMA>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
                                   &cmp_page_map);
         cp_async_wait<0>();
     } else {
         if (kRegsIssue < kRegsLaunch) registers_release<kRegsIssue>();
         if (warp >= kWarpQuery) {
-            query_loop<DEBUG>(p, dbg, sm, items, first, end, warp - kWarpQuery, lane);
+            query_loop<DEBUG>(p, dbg, sm, items, plan, warp - kWarpQuery, lane);
         } else {
             // the whole warp runs the issue loop and one elected lane issues: with converged control
             // flow the operand descriptors live in uniform registers, which halves the cost per MMA
-            if (warp == kWarpMma) mma_qk_loop(sm, items, first, end, tmem);
-            else mma_pv_loop(sm, items, first, end, tmem);
+            if (warp == kWarpMma) mma_qk_loop(sm, items, plan, tmem);
+            else mma_pv_loop(sm, plan, tmem);
             __syncwarp();
         }
     }
