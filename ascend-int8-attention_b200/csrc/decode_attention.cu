@@ -180,18 +180,21 @@ __device__ __forceinline__ uint32_t owner_of(const int32_t *cu, uint32_t live_ba
 // part); the arithmetic is in work_split.h.  The live shape comes from cuQ / seqLens on the device,
 // so a captured graph follows the live batch.  The pieces of tokens that fall into this CTA's range
 // of the flat tile list become its items, written to workspace entries no other CTA uses.
-// `scratch` is shared memory the roles do not use yet (the KV ring).
+// `sc` is shared memory the roles do not use yet (the KV ring).
+
+// What a CTA keeps of the plan (in shared memory of its own, written during plan_cta).
 struct PlanResult {
-    uint32_t first, end, live_tokens, tiles;      // this CTA's entries [first, end) and the tiles they hold
-    uint4 first_lo, first_hi;                     // its first item, so that no role starts with a global read
-};
-struct PlanScratch {
-    uint32_t scan[80];
-    uint32_t live, mismatch, first, count, head, tail, tiles, pad;
-    uint4 first_item[2];
-    int32_t cu[kPlanStaged];
+    uint32_t first, count;        // its items are the workspace entries [first, first + count), in token order
+    uint32_t live_tokens, tiles;  // live query tokens of the launch; tiles in this CTA's items
+    uint4 first_item[2];          // the item at entry `first`, so that no role starts with a global-memory read
 };
 static_assert(sizeof(PlanResult) == 48, "PlanResult has its own 48 bytes of shared memory");
+struct PlanScratch {
+    uint32_t scan[80];
+    uint32_t live, mismatch, pad[2];
+    int32_t cu[kPlanStaged];
+};
+
 template <int RATIO>
 __device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch *sc, PlanResult *result)
 {
@@ -202,7 +205,8 @@ __device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch
     Item *items = reinterpret_cast<Item *>(ws + kWsItems);
 
     if (tid == 0) {
-        sc->live = 0; sc->mismatch = 0xffffffffu; sc->first = 0xffffffffu; sc->count = 0; sc->head = 0; sc->tail = 0; sc->tiles = 0;
+        sc->live = 0; sc->mismatch = 0xffffffffu;
+        result->first = 0xffffffffu; result->count = 0; result->tiles = 0;
     }
     const bool staged = p.batch + 1u <= kPlanStaged;
     const int32_t seq_first = tid < p.batch ? seq[tid] : 0;      // in flight together with the cuQ reads
@@ -242,74 +246,51 @@ __device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch
     const uint32_t quota = split::quota_of(split::total_cost(total_tiles, live_tokens), grid);
     const uint32_t me = blockIdx.x;
 
-    // Only threads whose tokens overlap this CTA's range [me * quota, (me + 1) * quota) go on.  Two
-    // rounds over their tokens: the first finds where the CTA's entries begin, how many there are and
-    // whether the range begins / ends inside a token; the second writes the items.
-    //
-    // Order of a CTA's items.  A range that ends inside a token holds that token's first piece, and
-    // the CTA after it holds the next piece at the very front of its range.  Walked in token order
-    // the first piece would be the last thing this CTA does, and the split-K merge (partial state to
-    // global memory, ticket, the other pieces read back) would sit at the end of every CTA's
-    // critical path.  So that piece is moved up: a piece continued from the previous CTA first (it
-    // is the one the previous CTA is waiting for), then the piece continuing into the next CTA,
-    // then the whole tokens.  Both ends of a split token are then finished early in the kernel and
-    // the merge overlaps the tiles that follow.
+    // Only threads whose tokens overlap this CTA's range [me * quota, (me + 1) * quota) go on.  Items are
+    // written at their entries in token order; a thread remembers the first one it wrote.
     const uint32_t range_begin = split::first_tile_position(tile_base, t_begin) - split::kItemCost;
     const uint32_t range_end = split::first_tile_position(tile_base + my_tiles, t_end) - split::kItemCost;
-    const bool overlaps = range_begin < (me + 1) * quota && range_end > me * quota;
-#pragma unroll 1
-    for (int round = 0; round < 2; ++round) {
-        const uint32_t first = sc->first, count = sc->count;        // round 1: complete (read behind the barrier below)
-        const uint32_t head = sc->head ? 1u : 0u;
-        const bool rotate = round == 1 && sc->tail && count > head + 1u;
-        if (overlaps) {
-            uint32_t before = tile_base;
-            for (uint32_t t = t_begin; t < t_end; ++t) {
-                uint32_t batch; int32_t position;
-                const uint32_t n = tiles_of(t, batch, position);
-                const uint32_t start = split::first_tile_position(before, t);
-                const split::Pieces pc = split::pieces_of(start, n, quota);
-                if (me >= pc.first_cta && me < pc.first_cta + pc.count) {
-                    const uint32_t entry = split::item_index(t, me), part = me - pc.first_cta;
-                    if (round == 0) {
-                        atomicMin(&sc->first, entry);
-                        atomicAdd(&sc->count, 1u);
-                        if (part > 0) sc->head = 1u;                                  // continued from the previous CTA
-                        if (part + 1u < pc.count) sc->tail = 1u;                      // continues into the next CTA
-                    } else {
-                        uint32_t place = entry - first;                               // position in token order
-                        if (rotate) place = split::rotated_place(place, count, head);
-                        const split::TileRange r = split::piece_range(start, n, quota, me);
-                        uint4 *dst = reinterpret_cast<uint4 *>(items + first + place);
-                        const uint4 lo = make_uint4(t, batch, (uint32_t)position, r.begin);
-                        const uint4 hi = make_uint4(r.end, part, pc.count, pc.first_cta);
-                        dst[0] = lo;
-                        dst[1] = hi;
-                        if (place == 0) { sc->first_item[0] = lo; sc->first_item[1] = hi; }
-                        atomicAdd(&sc->tiles, r.end - r.begin);
-                    }
-                }
-                before += n;
+    uint32_t my_entry = 0xffffffffu;
+    uint4 my_lo = make_uint4(0, 0, 0, 0), my_hi = my_lo;
+    if (range_begin < (me + 1) * quota && range_end > me * quota) {
+        uint32_t before = tile_base, found = 0, tiles = 0;
+        for (uint32_t t = t_begin; t < t_end; ++t) {
+            uint32_t batch; int32_t position;
+            const uint32_t n = tiles_of(t, batch, position);
+            const uint32_t start = split::first_tile_position(before, t);
+            const split::Pieces pc = split::pieces_of(start, n, quota);
+            if (me >= pc.first_cta && me < pc.first_cta + pc.count) {
+                const uint32_t entry = split::item_index(t, me), part = me - pc.first_cta;
+                const split::TileRange r = split::piece_range(start, n, quota, me);
+                const uint4 lo = make_uint4(t, batch, (uint32_t)position, r.begin);
+                const uint4 hi = make_uint4(r.end, part, pc.count, pc.first_cta);
+                uint4 *dst = reinterpret_cast<uint4 *>(items + entry);
+                dst[0] = lo;
+                dst[1] = hi;
+                if (!found) { my_entry = entry; my_lo = lo; my_hi = hi; }
+                ++found;
+                tiles += r.end - r.begin;
             }
+            before += n;
         }
-        __syncthreads();
+        if (found) {
+            atomicMin(&result->first, my_entry);
+            atomicAdd(&result->count, found);
+            atomicAdd(&result->tiles, tiles);
+        }
     }
+    __syncthreads();
+    if (my_entry == result->first) { result->first_item[0] = my_lo; result->first_item[1] = my_hi; }
     if (tid == 0) {
-        PlanResult r;
-        r.first = sc->count ? sc->first : 0u;
-        r.end = r.first + sc->count;
-        r.live_tokens = live_tokens;
-        r.tiles = sc->tiles;
-        r.first_lo = sc->first_item[0];
-        r.first_hi = sc->first_item[1];
-        *result = r;
+        result->live_tokens = live_tokens;
+        if (result->count == 0) result->first = 0;
         if (me == 0) {
             PlanHeader *header = reinterpret_cast<PlanHeader *>(ws);
             header->live_batch = live_batch; header->live_tokens = live_tokens; header->total_tiles = total_tiles;
             header->quota = quota; header->n_items = live_tokens; header->grid = grid;
         }
     }
-    __syncthreads();          // the result is published and the scratch area is handed back to the KV ring
+    __syncthreads();          // the result is complete and the scratch area is handed back to the KV ring
 }
 // ------------------------------------------------------------------ decode kernel pieces
 struct Shared {
@@ -363,7 +344,7 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
 // Walks the CTA's tiles in order, keeping the next item's descriptor in flight so that moving
 // on to it does not expose a global-memory round trip.
 struct Cursor {
-    uint32_t item, items_end, j;
+    uint32_t k, j;              // k-th item of the CTA, tile j of it
     Item it;
     uint4 next_lo, next_hi;
     bool done;
@@ -375,32 +356,34 @@ __device__ __forceinline__ Item decode_item(const uint4 &a, const uint4 &b)
     it.tile_end = b.x; it.part = b.y; it.nparts = b.z; it.first_cta = b.w;
     return it;
 }
-__device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items)
+// The plan sits in shared memory; what a cursor needs of it is read when it moves to another item
+// and not kept in registers (the producer warps run on 56 of them).
+__device__ __forceinline__ void cursor_prefetch(Cursor &c, const Item *items, const PlanResult &plan)
 {
-    if (c.item + 1 < c.items_end) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(items + c.item + 1);
+    if (c.k + 1 < plan.count) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(items + plan.first + c.k + 1);
         c.next_lo = src[0];
         c.next_hi = src[1];
     }
 }
 __device__ __forceinline__ void cursor_init(Cursor &c, const Item *items, const PlanResult &plan)
 {
-    c.item = plan.first; c.items_end = plan.end; c.done = plan.first >= plan.end; c.j = 0;
+    c.k = 0; c.done = plan.count == 0; c.j = 0;
     c.next_lo = c.next_hi = make_uint4(0, 0, 0, 0);
     if (!c.done) {
-        c.it = decode_item(plan.first_lo, plan.first_hi);
+        c.it = decode_item(plan.first_item[0], plan.first_item[1]);
         c.j = c.it.tile_begin;
-        cursor_prefetch(c, items);
+        cursor_prefetch(c, items, plan);
     }
 }
 // Returns true when the cursor moved on to a new item.
-__device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items)
+__device__ __forceinline__ bool cursor_advance(Cursor &c, const Item *items, const PlanResult &plan)
 {
     if (++c.j < c.it.tile_end) return false;
-    if (++c.item >= c.items_end) { c.done = true; return false; }
+    if (++c.k >= plan.count) { c.done = true; return false; }
     c.it = decode_item(c.next_lo, c.next_hi);
     c.j = c.it.tile_begin;
-    cursor_prefetch(c, items);
+    cursor_prefetch(c, items, plan);
     return true;
 }
 // Trailing cursor of a producer warp: walks the same tiles as a leading Cursor, a bounded
@@ -443,22 +426,23 @@ __device__ __forceinline__ void follower_advance2(Follower &f, const Shared &sm,
     if (!f.done) follower_advance(f, sm, ring);
 }
 // Leading cursor: `steps` tiles on, publishing every item it enters; true when the item changed.
-__device__ __forceinline__ bool leader_advance(Cursor &c, const Item *items, const Shared &sm, uint32_t ring, uint32_t steps)
+__device__ __forceinline__ bool leader_advance(Cursor &c, const Item *items, const PlanResult &plan, const Shared &sm, uint32_t ring,
+                                               uint32_t steps)
 {
     bool moved = false;
     for (uint32_t s = 0; s < steps && !c.done; ++s) {
-        if (cursor_advance(c, items)) {
-            ring_put(sm, ring, c.item, c.it);
+        if (cursor_advance(c, items, plan)) {
+            ring_put(sm, ring, c.k, c.it);
             moved = true;
         }
     }
     return moved;
 }
 // Skip whatever is left of the current item.
-__device__ __forceinline__ void cursor_next_item(Cursor &c, const Item *items)
+__device__ __forceinline__ void cursor_next_item(Cursor &c, const Item *items, const PlanResult &plan)
 {
     c.j = c.it.tile_end - 1u;
-    cursor_advance(c, items);
+    cursor_advance(c, items, plan);
 }
 
 // ------------------------------------------------------------------ producer
@@ -554,11 +538,11 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                               const CUtensorMap *cmp_page_map)
 {
     // set 0 fetches tiles 0, 2, 4 ... of the CTA, set 1 tiles 1, 3, 5 ...
-    const uint32_t first = plan.first, end = plan.end;
+    const uint32_t first = 0, end = plan.count;      // the followers count the CTA's items from 0
     Cursor ca;
     cursor_init(ca, items, plan);
-    if (!ca.done) ring_put(sm, set, ca.item, ca.it);
-    if (set) leader_advance(ca, items, sm, set, 1);
+    if (!ca.done) ring_put(sm, set, ca.k, ca.it);
+    if (set) leader_advance(ca, items, plan, sm, set, 1);
     Follower cb, cc;
     follower_init(cb, sm, set, first, end);
     follower_init(cc, sm, set, first, end);
@@ -625,7 +609,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             int32_t cand_a = -1;
             if (!ca.done) {
                 cand_a = candidate_row<RATIO>(p, ca, comp, slot);
-                if (leader_advance(ca, items, sm, set, 2) && RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
+                if (leader_advance(ca, items, plan, sm, set, 2) && RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
             }
             cand[u] = cand_a;
         }
@@ -709,8 +693,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
     const bool leader = elect_one();
-    const uint32_t first = __shfl_sync(0xffffffffu, plan.first, 0);        // loop bounds the compiler can see are the same in all lanes
-    const uint32_t end = __shfl_sync(0xffffffffu, plan.end, 0);
+    const uint32_t first = 0, end = __shfl_sync(0xffffffffu, plan.count, 0);        // a loop bound the compiler can see is the same in all lanes
     Cursor cq;
     cursor_init(cq, items, plan);
     uint32_t t = 0;                        // tiles issued so far
@@ -760,7 +743,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
             }
             ++t;
         }
-        cursor_next_item(cq, items);
+        cursor_next_item(cq, items, plan);
     }
 }
 
@@ -866,7 +849,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
         const uint32_t uses_before = kind == 0 ? k : k >> 1;
         char *qdst = sm.ptr + kSmQ + qbuf * 8192u;
         const uint4 *src = reinterpret_cast<const uint4 *>(p.q + (uint64_t)it.token * 8192u) + lane * 2u;
-        if (cur.item + 1 < cur.items_end) {        // the next item's query rows start their way to L2 now
+        if (cur.k + 1 < plan.count) {        // the next item's query rows start their way to L2 now
             const char *next = reinterpret_cast<const char *>(p.q) + (uint64_t)cur.next_lo.x * 8192u + lane * 256u;
             asm volatile("prefetch.global.L2 [%0];" ::"l"(next));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(next + 128));
@@ -937,7 +920,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
             fence_proxy_async_smem();
         }
         mbar_arrive(sm.bar(kBarQReady + qbuf));
-        cursor_next_item(cur, items);
+        cursor_next_item(cur, items, plan);
     }
 }
 
@@ -1077,7 +1060,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 mbar_arrive(sm.bar(kBarItemDone + (k & 7u)));
             }
         }
-        cursor_next_item(cur, items);
+        cursor_next_item(cur, items, plan);
     }
 }
 
@@ -1200,34 +1183,38 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
                     out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fmul_rn(acc[mb][h], inv));
             }
             if (lse && ch < 8) lse[ch] = __fadd_rn(fin[ch], logf(fin[8 + ch]));
-            cursor_next_item(cur, items);
+            cursor_next_item(cur, items, plan);
             continue;
         }
 
         // ---------------- piece of a token shared with other CTAs
-        const uint32_t my_slot = split::partial_slot(it.first_cta, it.part);
-        float *mine = partials + (uint64_t)my_slot * kPartialFloats;
+        // Every piece writes its state to the workspace, makes it visible and then draws a ticket; the
+        // piece that draws the last one finds all states written and merges them in piece order (so the
+        // result does not depend on who arrives when).  Nobody waits for another CTA.
+        float *mine = partials + (uint64_t)split::partial_slot(it.first_cta, it.part) * kPartialFloats;
 #pragma unroll
         for (int h = 0; h < 8; ++h)
 #pragma unroll
             for (int mb = 0; mb < 4; ++mb) mine[h * 512 + mb * 128 + ch] = acc[mb][h];
         if (ch < 16) mine[4096 + ch] = fin[ch];
-        __threadfence();
+        // One thread draws the ticket with release / acquire semantics at GPU scope behind a barrier of
+        // the 128 writers: the barrier orders their stores before the draw, the release publishes
+        // them with it, the acquire (and the second barrier) orders the merger's reads behind it.
         if (!group_sync<1>(sm, 3, group_phase)) return;
-        if (ch == 0) misc[3] = atomicAdd(tickets + split::ticket_index(it.first_cta), 1u);
+        uint32_t *ticket = tickets + split::ticket_index(it.first_cta);
+        if (ch == 0) misc[3] = atomic_add_acq_rel(ticket, 1u);
         if (!group_sync<1>(sm, 3, group_phase)) return;
-        const uint32_t ticket = misc[3];
-        if (ticket + 1u == it.nparts) {
-            // last piece to arrive: merge, and leave the ticket at zero for the next launch (nobody
-            // else touches it any more in this one)
-            if (ch == 0) tickets[split::ticket_index(it.first_cta)] = 0u;
-            __threadfence();
+        if (misc[3] + 1u == it.nparts) {
+            // the ticket goes back to zero for the next launch (nobody else touches it any more in this one)
+            if (ch == 0) *ticket = 0u;
+            // The loops over the pieces are unrolled so that the loads of several pieces are in flight
+            // together: a merge is a chain of L2 round trips at the very end of a CTA's work.
             float top[8], den[8];
 #pragma unroll
             for (int h = 0; h < 8; ++h) { top[h] = -INFINITY; den[h] = 0.f; }
+#pragma unroll 4
             for (uint32_t q = 0; q < it.nparts; ++q) {
-                const uint32_t sl = split::partial_slot(it.first_cta, q);
-                const float *pm = partials + (uint64_t)sl * kPartialFloats + 4096;
+                const float *pm = partials + (uint64_t)split::partial_slot(it.first_cta, q) * kPartialFloats + 4096;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) top[h] = fmaxf(top[h], __ldcg(pm + h));
             }
@@ -1235,9 +1222,9 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
             for (int mb = 0; mb < 4; ++mb)
 #pragma unroll
                 for (int h = 0; h < 8; ++h) acc[mb][h] = 0.f;
+#pragma unroll 2
             for (uint32_t q = 0; q < it.nparts; ++q) {
-                const uint32_t sl = split::partial_slot(it.first_cta, q);
-                const float *ps = partials + (uint64_t)sl * kPartialFloats;
+                const float *ps = partials + (uint64_t)split::partial_slot(it.first_cta, q) * kPartialFloats;
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
                     const float g = expf(__fsub_rn(__ldcg(ps + 4096 + h), top[h]));
@@ -1261,7 +1248,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
                 lse[ch] = __fadd_rn(mm, logf(ll));
             }
         }
-        cursor_next_item(cur, items);
+        cursor_next_item(cur, items, plan);
     }
 }
 

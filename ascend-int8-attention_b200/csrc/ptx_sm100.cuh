@@ -59,6 +59,16 @@ __device__ __forceinline__ void grid_dependency_launch_dependents()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// ---------------------------------------------------------------- release / acquire on global memory
+// Fetch-and-add that publishes every write ordered before it (this thread's, and those of other
+// threads it has synchronised with) to the GPU, and orders later reads behind the value it returns.
+__device__ __forceinline__ uint32_t atomic_add_acq_rel(uint32_t *address, uint32_t value)
+{
+    uint32_t old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(address), "r"(value) : "memory");
+    return old;
+}
+
 // ---------------------------------------------------------------- cp.async (16-byte, L2 only)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
 {

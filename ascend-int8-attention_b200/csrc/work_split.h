@@ -95,17 +95,6 @@ SHAREDKV_HD TileRange piece_range(uint32_t start, uint32_t tiles, uint32_t quota
 // and increases along (token, piece); a CTA's items are consecutive entries.
 SHAREDKV_HD uint32_t item_index(uint32_t token, uint32_t cta) { return token + cta; }
 
-// Processing order of a CTA's `count` items.  In token order a piece that continues into the next
-// CTA comes last; it is moved up behind the piece continued from the previous CTA (`head` = 1 when
-// there is one, else 0), so that both ends of a split token are finished early and its merge does
-// not end the CTA.  Maps a position in token order to the position in processing order; call only
-// when the last item in token order continues into the next CTA and count > head + 1.
-SHAREDKV_HD uint32_t rotated_place(uint32_t place, uint32_t count, uint32_t head)
-{
-    if (place < head) return place;
-    return place == count - 1u ? head : place + 1u;
-}
-
 // Partial-state slot of piece `part` of a token whose first piece is in CTA `first_cta`.  A CTA
 // holds at most one piece that continues into the next CTA (part 0 of some token, or a middle
 // piece) and at most one that continues from the previous CTA, hence two slots per CTA: the odd

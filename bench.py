@@ -374,9 +374,11 @@ class WriterBench:
             op.run()
         torch.cuda.synchronize(device)
         self.step_graphs = [capture(device, lambda c=c: self.step(c)) for c in range(copies)]
+        # one step per rotating set in ONE graph, as a serving step holds the writes of all its layers
+        self.round_graph = capture(device, lambda: [self.step(c) for c in range(copies)])
         self.size_graphs = [capture(device, lambda k=k: [self.ops[c * self.per_step + k].run() for c in range(copies)])
                             for k in range(self.per_step)]
-        for g in self.step_graphs + self.size_graphs:
+        for g in self.step_graphs + self.size_graphs + [self.round_graph]:
             g.replay()
         torch.cuda.synchronize(device)
 
@@ -388,15 +390,16 @@ class WriterBench:
         """Step time from replays of the step graphs for about `seconds`; per launch size from replays
         of the per-size graphs.  Returns a dict of figures (device time, one rank)."""
         peak, peak_kind = measured_peaks()
-        probe_a, probe_b = timed(lambda i: self.step_graphs[i % self.copies].replay(), 8)
+        probe_a, probe_b = timed(lambda i: self.round_graph.replay(), 2)
         torch.cuda.synchronize(self.device)
-        steps = max(8, int(seconds * 1000 / max(probe_a.elapsed_time(probe_b) / 8, 1e-3)))
-        a, b = timed(lambda i: self.step_graphs[i % self.copies].replay(), steps)
+        rounds = max(2, int(seconds * 1000 / max(probe_a.elapsed_time(probe_b) / 2, 1e-3)))
+        a, b = timed(lambda i: self.round_graph.replay(), rounds)
         torch.cuda.synchronize(self.device)
+        steps = rounds * self.copies
         step_ms = a.elapsed_time(b) / steps
         sizes = {}
         for k, (rows, _) in enumerate(WRITER_ROWS):
-            reps = max(4, steps // (4 * self.copies))
+            reps = max(4, rounds // 4)
             a, b = timed(lambda i, k=k: self.size_graphs[k].replay(), reps)
             torch.cuda.synchronize(self.device)
             ms = a.elapsed_time(b) / (reps * self.copies)

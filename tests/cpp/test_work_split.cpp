@@ -135,20 +135,6 @@ int main(int argc, char **argv)
                 const auto found = entries.find(cta_first[cta] + i);
                 REQUIRE(found != entries.end() && found->second == cta);
             }
-            // processing order: a permutation of the CTA's entries that keeps a piece continued from the
-            // previous CTA first and puts the piece continuing into the next CTA right behind it
-            const uint32_t count = cta_items[cta], head = cta_head[cta];
-            if (cta_tail[cta] && count > head + 1) {
-                std::vector<uint8_t> taken(count, 0);
-                for (uint32_t i = 0; i < count; ++i) {
-                    const uint32_t place = rotated_place(i, count, head);
-                    REQUIRE(place < count && !taken[place]);
-                    taken[place] = 1;
-                    if (i < head) REQUIRE(place == i);
-                    else if (i == count - 1) REQUIRE(place == head);
-                    else REQUIRE(place == i + 1);
-                }
-            }
         }
     }
     std::printf("work split ok: %u workloads, %llu pieces, %llu split tokens\n", workloads, pieces_seen, split_tokens);
