@@ -82,6 +82,10 @@ int sharedkv_workspace_status(const void *workspace, void *stream)
     return sharedkv::workspace_status(workspace, static_cast<cudaStream_t>(stream));
 }
 
+int launch_sharedkv(uint32_t, void *stream, const SharedKVArgs *args)
+{
+    return sharedkv::attention(SHAREDKV_VARIANT_GENERAL, args, static_cast<cudaStream_t>(stream), nullptr);
+}
 int launch_sharedkv_c8_sparse(uint32_t, void *stream, const SharedKVArgs *args)
 {
     return sharedkv::attention(SHAREDKV_VARIANT_C4, args, static_cast<cudaStream_t>(stream), nullptr);

@@ -162,6 +162,12 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *s
     return result;
 }
 
+// Tiles of the original kind in front of a token's compressed tiles (uniform over a launch).
+__device__ __forceinline__ uint32_t original_tiles(const SharedKVArgs &p)
+{
+    return split::original_tiles(p.oriIndices != 0, p.oriTopk);
+}
+
 // ------------------------------------------------------------------ work split
 constexpr uint32_t kPlanStaged = 11776;      // cuQ entries kept in shared memory (46 KB)
 
@@ -231,10 +237,11 @@ __device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch
     // counts gives every thread its flat tile offset and the CTA the total (hence the quota).
     const uint32_t per = (live_tokens + kThreads - 1) / kThreads;
     const uint32_t t_begin = min(tid * per, live_tokens), t_end = min(t_begin + per, live_tokens);
+    const uint32_t ori_tiles = original_tiles(p);
     auto tiles_of = [&](uint32_t t, uint32_t &batch, int32_t &position) {
         batch = one_each ? t : owner_of(cu, live_batch, t);
         position = split::token_position(seq[batch], cu[batch + 1], t);
-        return split::tiles_of_token(RATIO, position, p.topk);
+        return split::tiles_of_token(p.ratio, position, p.topk, ori_tiles);      // p.ratio: a ratio-1 layer runs the C128 kernel without compressed tiles
     };
     uint32_t my_tiles = 0;
     for (uint32_t t = t_begin; t < t_end; ++t) {
@@ -494,15 +501,22 @@ __device__ __noinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s
 // Values read from the top-k array are returned unchecked (stage B range-checks them, so
 // that the load is not consumed here); every other path returns a valid row or -1.
 template <int RATIO>
-__device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot)
+__device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot,
+                                                 uint32_t ori_tiles)
 {
     const Item &it = c.it;
     if (it.position < 0) return -1;
-    if (c.j == 0) {
+    if (c.j < ori_tiles) {
+        if (p.oriIndices) {
+            // the caller's own list of physical slots of the original cache (reference.py:235-239):
+            // holes keep their place, stage B range-checks the value
+            const uint32_t s = c.j * kTileKeys + slot;
+            return s < p.oriTopk ? reinterpret_cast<const int32_t *>(p.oriIndices)[(uint64_t)it.token * p.oriTopk + s] : -1;
+        }
         const uint32_t n = min((uint32_t)it.position + 1u, kWindow);
         return slot < n ? (int32_t)((uint32_t)it.position + 1u - n + slot) : -1;
     }
-    const uint32_t s = (c.j - 1u) * kTileKeys + slot;
+    const uint32_t s = (c.j - ori_tiles) * kTileKeys + slot;
     if (RATIO == 128) return s < (uint32_t)(it.position + 1) / 128u ? (int32_t)s : -1;
     const int32_t *ix = reinterpret_cast<const int32_t *>(p.indices) + (uint64_t)it.token * p.topk;
     if (k.active) {
@@ -550,6 +564,8 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
         follower_advance(cb, sm, set);
         follower_advance(cc, sm, set);
     }
+    const uint32_t ori_tiles = original_tiles(p);
+    const bool explicit_slots = p.oriIndices != 0;
     Compaction comp;
     comp.active = false; comp.mask = comp.inclusive = comp.total = 0;
     if (RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
@@ -590,16 +606,21 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             // ---- stage B: range check and page-table lookup for tile n - kLookahead
             int32_t off_b = -1, page_b = 0;
             if (n >= (uint32_t)kLookahead && !cb.done) {
-                const bool ori = cb.j == 0;
-                const uint32_t limit = ori ? 0x7fffffffu
-                                           : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
+                const bool ori = cb.j < ori_tiles;
                 const int32_t c = cand[u];
-                // a row beyond the request's page-table row is no key (a sequence length larger
-                // than the table can describe must not read the next request's entries)
-                if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
-                    off_b = (c & 31) | (ori ? 256 : 0);
-                    page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
-                                 : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
+                if (ori && explicit_slots) {
+                    // a physical slot: page and row come from the value itself, no table is read
+                    if (c >= 0 && ((uint32_t)c >> 5) < p.oriPages) { off_b = (c & 31) | 256; page_b = c >> 5; }
+                } else {
+                    const uint32_t limit = ori ? 0x7fffffffu
+                                               : (cb.position < 0 ? 0u : (uint32_t)(cb.position + 1) / (uint32_t)RATIO);
+                    // a row beyond the request's page-table row is no key (a sequence length larger
+                    // than the table can describe must not read the next request's entries)
+                    if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
+                        off_b = (c & 31) | (ori ? 256 : 0);
+                        page_b = ori ? ori_table[(uint64_t)cb.batch * p.oriTableWidth + ((uint32_t)c >> 5)]
+                                     : cmp_table[(uint64_t)cb.batch * p.cmpTableWidth + ((uint32_t)c >> 5)];
+                    }
                 }
                 follower_advance2(cb, sm, set);
             }
@@ -608,7 +629,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             // ---- stage A: candidate row for tile n
             int32_t cand_a = -1;
             if (!ca.done) {
-                cand_a = candidate_row<RATIO>(p, ca, comp, slot);
+                cand_a = candidate_row<RATIO>(p, ca, comp, slot, ori_tiles);
                 if (leader_advance(ca, items, plan, sm, set, 2) && RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
             }
             cand[u] = cand_a;
@@ -621,7 +642,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             const uint32_t t = 2u * issued + set;          // position of the tile in the CTA's sequence
             const uint32_t stage = t % kStages, pass = t / kStages;
             if (!wait_phase<2>(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
-            const bool ori = cc.j == 0;
+            const bool ori = cc.j < ori_tiles;
             const int32_t id = row_ring[u * 32];
             const bool valid = id != kRowsInMap;
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
@@ -689,7 +710,7 @@ drain:
 // retires one per ~40, so the two products of a tile are issued by two threads of different
 // warps (different SM sub-partitions): S = K.Q^T by one, O = K^T.P by the other.  Each product is
 // 16 instructions of M = 128, N = 16, K = 32 bytes.
-__device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
+__device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem, uint32_t ori_tiles)
 {
     constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
     const bool leader = elect_one();
@@ -698,13 +719,14 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
     cursor_init(cq, items, plan);
     uint32_t t = 0;                        // tiles issued so far
     for (uint32_t k = 0; k < end - first; ++k) {
-        // Query codes: one buffer for the original kind (read by an item's first tile only) and two
+        // Query codes: one buffer for the original kind (read by an item's original tiles only) and two
         // alternating buffers for the compressed kind, so that the next item is encoded while this
         // one is processed.  Per item and kind this thread waits once for "encoded" and signals once
         // "no longer read" (a commit behind the last MMA that reads the buffer, or a plain arrival
         // when the item has no tile of that kind).
         const uint32_t tile_begin = __shfl_sync(0xffffffffu, cq.it.tile_begin, 0), tile_end = __shfl_sync(0xffffffffu, cq.it.tile_end, 0);
-        const bool uses_ori = tile_begin == 0, uses_cmp = tile_end > max(tile_begin, 1u);
+        const bool uses_ori = tile_begin < ori_tiles, uses_cmp = tile_end > max(tile_begin, ori_tiles);
+        const uint32_t last_ori = min(tile_end, ori_tiles) - 1u;       // only meaningful when uses_ori
         const uint32_t last = tile_end - 1u;
         uint32_t j = tile_begin;
         const uint32_t cbuf = 1u + (k & 1u), cphase = (k >> 1) & 1u;     // compressed-kind buffer of this item
@@ -717,7 +739,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
         }
         for (; j < tile_end; ++j) {
             const uint32_t stage = t % kStages, buf = t & 1u, ph = (t >> 1) & 1u;
-            if (j != 0 && !cmp_ready) {
+            if (j >= ori_tiles && !cmp_ready) {
                 if (!wait_phase<3>(sm, kBarQReady + cbuf, cphase)) return;
                 cmp_ready = true;
             }
@@ -725,7 +747,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
             if (!wait_phase<3>(sm, kBarSFree + buf, ph ^ 1u)) return;
             tc_fence_after();
             const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-            const uint32_t qb = sm.base + kSmQ + (j == 0 ? 0u : cbuf * 8192u);
+            const uint32_t qb = sm.base + kSmQ + (j < ori_tiles ? 0u : cbuf * 8192u);
             const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
             // the address field counts 16-byte units; offsets stay inside the 14-bit field
 #pragma unroll 1
@@ -738,7 +760,7 @@ __device__ void mma_qk_loop(const Shared &sm, const Item *items, const PlanResul
             }
             if (leader) mma_commit(sm.bar(kBarSFull + buf));
             if (leader) {
-                if (j == 0) mma_commit(sm.bar(kBarQFree + 0));
+                if (j < ori_tiles) { if (j == last_ori) mma_commit(sm.bar(kBarQFree + 0)); }
                 else if (j == last) mma_commit(sm.bar(kBarQFree + cbuf));
             }
             ++t;
@@ -839,11 +861,12 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
             sc[4 * i] = v.x; sc[4 * i + 1] = v.y; sc[4 * i + 2] = v.z; sc[4 * i + 3] = v.w;
         }
     }
+    const uint32_t ori_tiles = original_tiles(p);
     Cursor cur;
     cursor_init(cur, items, plan);
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
-        const bool used = kind == 0 ? it.tile_begin == 0 : it.tile_end > max(it.tile_begin, 1u);
+        const bool used = kind == 0 ? it.tile_begin < ori_tiles : it.tile_end > max(it.tile_begin, ori_tiles);
         // buffer, and the use of it that must be over before it is rewritten
         const uint32_t qbuf = kind == 0 ? 0u : 1u + (k & 1u);
         const uint32_t uses_before = kind == 0 ? k : k >> 1;
@@ -939,6 +962,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
     float sink[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) sink[i] = reinterpret_cast<const float *>(p.sinks)[half * 4u + i];
+    const uint32_t ori_tiles = original_tiles(p);
 
     Cursor cur;
     cursor_init(cur, items, plan);
@@ -956,7 +980,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
             l[i] = (key == 0 && it.tile_begin == 0) ? 1.f : 0.f;
         }
         for (uint32_t j = it.tile_begin; j < it.tile_end; ++j, ++gt) {
-            const uint32_t kind = j == 0 ? 0u : 1u;
+            const uint32_t kind = j < ori_tiles ? 0u : 1u;
             const uint32_t stage = gt % kStages, buf = gt & 1u, ph = (gt >> 1) & 1u;
             if (!wait_phase<0>(sm, kBarFull + stage, (gt / kStages) & 1u)) return;
             const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
@@ -979,7 +1003,7 @@ __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, co
                 if (rec < dbg.maxTiles) {
                     if (threadIdx.x == 0) {
                         int32_t *info = reinterpret_cast<int32_t *>(dbg.tileInfo) + (uint64_t)rec * 4u;
-                        info[0] = (int32_t)it.token; info[1] = (int32_t)kind; info[2] = (int32_t)(kind ? j - 1u : 0u); info[3] = (int32_t)it.part;
+                        info[0] = (int32_t)it.token; info[1] = (int32_t)kind; info[2] = (int32_t)(kind ? j - ori_tiles : j); info[3] = (int32_t)it.part;
                     }
                     if (half == 0 && lane == 0) reinterpret_cast<uint32_t *>(dbg.validMask)[(uint64_t)rec * 4u + warp] = mask_word;
                     int32_t *g = reinterpret_cast<int32_t *>(dbg.qkAcc) + ((uint64_t)rec * 128u + key) * 16u;
@@ -1109,6 +1133,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
         }
     }
 
+    const uint32_t ori_tiles = original_tiles(p);
     Cursor cur;
     cursor_init(cur, items, plan);
     uint32_t gt = 0;
@@ -1156,7 +1181,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 #pragma unroll
                         for (int i = 0; i < 4; ++i) g[i] = make_uint4(o[q][4 * i], o[q][4 * i + 1], o[q][4 * i + 2], o[q][4 * i + 3]);
                     }
-                    const float s = j == 0 ? sc[0][mb] : sc[1][mb];
+                    const float s = j < ori_tiles ? sc[0][mb] : sc[1][mb];
 #pragma unroll
                     for (int h = 0; h < 8; ++h) {
                         const float dots = __fmaf_rn(small_int_to_float(o[q][8 + h]), kInv127, small_int_to_float(o[q][h]));
@@ -1334,7 +1359,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         } else {
             // the whole warp runs the issue loop and one elected lane issues: with converged control
             // flow the operand descriptors live in uniform registers, which halves the cost per MMA
-            if (warp == kWarpMma) mma_qk_loop(sm, items, plan, tmem);
+            if (warp == kWarpMma) mma_qk_loop(sm, items, plan, tmem, original_tiles(p));
             else mma_pv_loop(sm, plan, tmem);
             __syncwarp();
         }
@@ -1502,14 +1527,23 @@ int workspace_status(const void *workspace, cudaStream_t stream)
 int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, const SharedKVDebug *debug)
 {
     if (args == nullptr) return SHAREDKV_EINVAL;
-    if (variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
+    const bool general = variant == SHAREDKV_VARIANT_GENERAL;
+    if (!general && variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
         return SHAREDKV_EVARIANT;
-    const SharedKVArgs a = *args;
+    SharedKVArgs a = *args;
     if (a.tokens == 0 || a.batch == 0) return SHAREDKV_OK;
-    const uint32_t ratio = variant == SHAREDKV_VARIANT_C128 ? 128u : 4u;
-    if (a.ratio != ratio || a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage || a.cmpBlock != kPage ||
-        a.oriIndices != 0)
-        return SHAREDKV_EINVAL;
+    // The C4 / C128 entries take their own ratio and no explicit original slots, as the reference's
+    // do; the general entry takes ratio 1 (no compressed cache), 4 or 128, with or without them.
+    const uint32_t ratio = general ? a.ratio : (variant == SHAREDKV_VARIANT_C128 ? 128u : 4u);
+    if (a.ratio != ratio || (ratio != 1u && ratio != 4u && ratio != 128u) || (!general && a.oriIndices != 0)) return SHAREDKV_EINVAL;
+    if (a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage) return SHAREDKV_EINVAL;
+    if (a.oriIndices && (a.oriTopk == 0 || a.oriIndices % 4u)) return SHAREDKV_EINVAL;
+    if (ratio == 1u) {
+        // no compressed kind: its fields alias the original cache so that nothing in the kernel is null
+        a.cmp = a.ori; a.cmpScale = a.oriScale; a.cmpTable = a.oriTable; a.cmpStride = a.oriStride;
+        a.cmpBlock = a.oriBlock; a.cmpTableWidth = a.oriTableWidth;
+    }
+    if (a.cmpBlock != kPage) return SHAREDKV_EINVAL;
     if (ratio == 4 && (a.topk == 0 || a.topk > 1024u || !a.indices || a.indices % 4u)) return SHAREDKV_EINVAL;
     if (!a.q || !a.ori || !a.cmp || !a.oriScale || !a.cmpScale || !a.oriTable || !a.cmpTable || !a.cuQ || !a.seqLens ||
         !a.sinks || !a.out || !a.workspace)

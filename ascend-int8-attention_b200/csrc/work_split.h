@@ -44,16 +44,24 @@ SHAREDKV_HD int32_t token_position(int32_t seq_len, int32_t cu_next, uint32_t to
     return seq_len - (cu_next - (int32_t)token);
 }
 
-// 128-key tiles of one token: the window tile plus the compressed tiles.  A C4 token that sees
-// at least one compressed row walks the whole top-k list (invalid selections are masked, not
-// skipped); a C128 token walks its prefix.  A token at a negative position still gets its window
-// tile so that its output row is written (as zeros with LSE = sink).
-SHAREDKV_HD uint32_t tiles_of_token(uint32_t ratio, int32_t position, uint32_t topk)
+// Tiles of the original kind per token: one (the 128-row window), or, when the caller names the
+// original rows itself, one per 128 entries of its slot list (reference.py:235-239 of the reference).
+SHAREDKV_HD uint32_t original_tiles(bool explicit_slots, uint32_t ori_topk)
 {
-    if (position < 0) return 1;
+    return explicit_slots ? (ori_topk + kTileKeys - 1) / kTileKeys : 1u;
+}
+
+// 128-key tiles of one token: the original tiles, then the compressed tiles.  A C4 token that sees
+// at least one compressed row walks the whole top-k list (invalid selections are masked, not
+// skipped); a C128 token walks its prefix; a ratio-1 layer has no compressed cache.  A token at a
+// negative position still gets its original tiles so that its output row is written (as zeros with
+// LSE = sink).
+SHAREDKV_HD uint32_t tiles_of_token(uint32_t ratio, int32_t position, uint32_t topk, uint32_t ori_tiles)
+{
+    if (position < 0 || ratio == 1) return ori_tiles;
     const uint32_t count = (uint32_t)(position + 1) / ratio;
-    if (ratio == 4) return 1 + (count ? (topk + kTileKeys - 1) / kTileKeys : 0);
-    return 1 + (count + kTileKeys - 1) / kTileKeys;
+    if (ratio == 4) return ori_tiles + (count ? (topk + kTileKeys - 1) / kTileKeys : 0);
+    return ori_tiles + (count + kTileKeys - 1) / kTileKeys;
 }
 
 SHAREDKV_HD uint32_t total_cost(uint32_t total_tiles, uint32_t live_tokens) { return total_tiles + kItemCost * live_tokens; }

@@ -22,7 +22,7 @@ _COUNT_FIELDS = ("tokens", "heads", "batch", "oriBlock", "cmpBlock", "oriTableWi
 # argument-struct pointer <- attribute of the case, for everything a rebind may replace
 _CASE_POINTERS = (("q", "q"), ("ori", "ori"), ("cmp", "cmp"), ("oriTable", "ori_block_table"),
                   ("cmpTable", "cmp_block_table"), ("indices", "cmp_indices"), ("cuQ", "cu_q"),
-                  ("seqLens", "seq_lens"), ("sinks", "sink"))
+                  ("seqLens", "seq_lens"), ("sinks", "sink"), ("oriIndices", "ori_indices"))
 
 
 class _Args(ctypes.Structure):
@@ -77,8 +77,10 @@ def _check_case(case, ori_scale, cmp_scale):
         _require(tensor.dtype == dtype and tensor.device == device and tensor.is_contiguous(),
                  "Invalid metadata dtype, device or contiguity")
     _require(picks is None or picks.device == device, "Indices must be on the same GPU")
-    _require(case.ori_indices is None,
-             "Explicit original slots (ori_indices) are outside the C4/C128 decode path built for CUDA")
+    slots = case.ori_indices
+    _require(slots is None or (slots.ndim == 3 and tuple(slots.shape[:2]) == (tokens, 1) and slots.shape[-1] > 0
+                               and slots.dtype == torch.int32 and slots.device == device and slots.is_contiguous()),
+             "Original physical slots must be contiguous INT32[T,1,K] on the query device")
     return tokens, heads, device
 
 
@@ -107,9 +109,11 @@ class PreparedAttention:
                  "Host-selected Ascend tile plans have no CUDA counterpart; leave them unset")
         self.query_group, self.tile_size, self.splits = 1, 128, 1
         self.adaptive_splits = self.trim_cube_tails = self.dynamic_grouped_c128 = False
-        self.dynamic_c4, self.dynamic_c128 = case.ratio == 4, case.ratio == 128
+        general = case.ratio == 1 or case.ori_indices is not None      # the reference's compatibility entry (variant 0)
+        self.dynamic_c4, self.dynamic_c128 = case.ratio == 4 and not general, case.ratio == 128 and not general
         _require(max_seq_len is None or (isinstance(max_seq_len, int) and max_seq_len > 0
-                                         and max_seq_len <= case.ori_block_table.shape[1] * case.ori.shape[1]
+                                         and (case.ori_indices is not None
+                                              or max_seq_len <= case.ori_block_table.shape[1] * case.ori.shape[1])
                                          and (case.ratio == 1 or max_seq_len // case.ratio
                                               <= case.cmp_block_table.shape[1] * case.cmp.shape[1])),
                  "max_seq_len exceeds what the block tables can address")
@@ -129,8 +133,8 @@ class PreparedAttention:
                  "No legacy INT8 kernels exist in the CUDA build: SHAREDKV_C8_DECODE=0 and "
                  "implementation='fallback' cannot be honoured")
         _require(c8_attention.supported(self),
-                 "This geometry is outside the CUDA C4/C128 decode kernels: need 8 heads, window 128, "
-                 "32-row pages, ratio 4 (top-k <= 1024) or ratio 128")
+                 "This geometry is outside the CUDA decode kernels: need 8 heads, window 128, 32-row pages, "
+                 "ratio 1, ratio 4 (top-k <= 1024) or ratio 128")
         self.__dict__.update(c8_attention.prepare(self, scratch_allocator=scratch_allocator).__dict__)
 
     def _bind_outputs(self, output, lse_output, return_lse, tokens, heads, device):
@@ -159,6 +163,7 @@ class PreparedAttention:
         args.tokens, args.heads, args.batch = tokens, heads, case.seq_lens.numel()
         args.ratio, args.window, args.splits = case.ratio, case.window, 1
         args.topk = case.cmp_indices.shape[-1] if case.cmp_indices is not None else 0
+        args.oriTopk = case.ori_indices.shape[-1] if case.ori_indices is not None else 0
         args.softmaxScale = case.softmax_scale
         return args
 

@@ -21,7 +21,7 @@ DIM = 512
 MAX_SPLITS = CORES          # a token's KV may be spread over at most one piece per CTA
 _MAX_CTAS = 160             # partial-result slots the library reserves
 _PARTIAL_FLOATS = HEADS * DIM + 16
-_VARIANTS = {"sparse": 20, "dense": 21, "sparse_small": 22}     # kernel ids of the host bridge
+_VARIANTS = {"general": 0, "sparse": 20, "dense": 21, "sparse_small": 22}     # kernel ids of the host bridge
 _SMALL_C4_TOKENS = 24       # below this the reference selects its "small" C4 image (c4_small.cpp:21)
 
 
@@ -61,19 +61,24 @@ def library():
 
 
 def supported(entry):
-    """True for the geometry the CUDA kernels implement: eight heads, window 128, 32-row pages, no
-    explicit original slots, ratio 128 or ratio 4 with at most 1024 selections per token."""
+    """True for the geometry the CUDA kernels implement: eight heads, window 128, 32-row pages;
+    ratio 128, ratio 4 with at most 1024 selections per token, or ratio 1 (original cache only);
+    with or without explicit original slots.  (The reference's C4/C128 route refuses explicit slots
+    and ratio 1, c8_attention.py:56-74, and leaves them to its general kernel; here one kernel family
+    serves both, through the general launcher.)"""
     args = getattr(entry, "args", None)
     if not getattr(entry, "blocks", 0) or not isinstance(args, argument_type()):
         return False
-    if args.tokens == 0 or args.batch == 0 or args.oriIndices:
+    if args.tokens == 0 or args.batch == 0 or (args.oriIndices and not args.oriTopk):
         return False
-    if (args.heads, args.window, args.oriBlock, args.cmpBlock) != (HEADS, 128, 32, 32):
+    if (args.heads, args.window, args.oriBlock) != (HEADS, 128, 32) or (args.ratio != 1 and args.cmpBlock != 32):
         return False
-    return args.ratio == 128 or (args.ratio == 4 and 0 < args.topk <= 1024)
+    return args.ratio in (1, 128) or (args.ratio == 4 and 0 < args.topk <= 1024)
 
 
 def _launcher_name(args):
+    if args.ratio == 1 or args.oriIndices:
+        return "general"
     if args.ratio == 128:
         return "dense"
     return "sparse_small" if args.tokens < _SMALL_C4_TOKENS else "sparse"
@@ -117,7 +122,7 @@ def prepare(entry, *, scratch_allocator=None, shared_storage=False):
     bound.argument_address = ctypes.addressof(bound.args)
     name = _launcher_name(bound.args)
     bound._c8_library = library()
-    bound.launch = getattr(bound._c8_library, "launch_sharedkv_c8_" + name)
+    bound.launch = getattr(bound._c8_library, "launch_sharedkv" if name == "general" else "launch_sharedkv_c8_" + name)
     bound.variant = _VARIANTS[name]
     bound.native = native_host(os.environ.get("SHAREDKV_HOST_QUEUE") == "1")
     if bound.native is not None and bound.native.attention_args_size != ctypes.sizeof(type(bound.args)):

@@ -77,7 +77,8 @@ typedef struct SharedKVArgs {
     uint64_t oriStride;  /* bytes between original pages (>= oriBlock * 512)         */
     uint64_t cmpStride;  /* bytes between compressed pages                           */
     uint64_t partial;    /* unused by this library (kept for layout compatibility)   */
-    uint64_t oriIndices; /* must be 0: explicit original slots are not on this path  */
+    uint64_t oriIndices; /* INT32 [tokens, 1, oriTopk] physical slots of the original
+                            cache attended instead of the window, or 0 (general entry only) */
     uint32_t tokens, heads, batch, oriBlock, cmpBlock, oriTableWidth, cmpTableWidth;
     uint32_t ratio, window, topk, splits, oriTopk, oriPages;
     float softmaxScale;
@@ -100,8 +101,9 @@ enum {
     SHAREDKV_ETIMEDOUT = -110  /* sharedkv_workspace_status: a device-side wait ran out */
 };
 
-/* Kernel variants of the host bridge (c8_launch.cpp:12-18). */
-enum { SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
+/* Kernel variants of the host bridge: 0 is the reference's general 128-key-tile kernel
+ * (launch.cpp:33), 20-22 its C4 / C128 decode kernels (c8_launch.cpp:12-18). */
+enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
 
 /* sizeof(SharedKVArgs) / sizeof(CacheWriteArgs) as compiled into the library; the
  * Python layer compares them with its ctypes mirrors (attention.py:223-226,
@@ -134,6 +136,14 @@ SHAREDKV_API int sharedkv_workspace_init(void *workspace, void *stream);
  * cudaError_t.  It is a diagnostic: nothing on the launch path calls it.  The reference reports
  * device failures through its runtime's stream errors instead. */
 SHAREDKV_API int sharedkv_workspace_status(const void *workspace, void *stream);
+
+/* General entry: args->ratio 1 (original cache only: the draft / sliding-window layers), 4 or 128,
+ * and, when args->oriIndices is set, the original rows named by the caller instead of the
+ * window: INT32 physical slots (page = slot / 32, row = slot % 32, no block-table lookup),
+ * oriTopk per query token, negative or out-of-range entries masked in place.  The same kernel as
+ * the entries below.  Replaces csrc/kernels/sharedkv.cpp:585 (`launch_sharedkv`, variant 0 of
+ * csrc/host/launch.cpp:33), the reference's kernel for everything outside its C4 / C128 route. */
+SHAREDKV_API int launch_sharedkv(uint32_t blocks, void *stream, const SharedKVArgs *args);
 
 /* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
  * query token.  `blocks` is accepted for signature compatibility and ignored: the

@@ -89,24 +89,38 @@ def _paged_rows(cache, table, batch, logical):
     return cache[pages, logical % block, 0, :]
 
 
+def _slot_rows(cache, slots):
+    """Rows named by physical slot, no block-table lookup   (reference.py:88-90)."""
+    block = cache.shape[1]
+    return cache[slots // block, slots % block, 0, :]
+
+
 @dataclass
 class Selection:
     """What one query token attends to (before tiling)."""
     token: int
     batch: int
     position: int
-    ori_index: torch.Tensor          # logical original rows, ascending
+    ori_index: torch.Tensor          # logical original rows, ascending; or the caller's physical slots, in list order
     cmp_index: torch.Tensor | None   # logical compressed rows in slot order (may hold invalid entries)
     cmp_valid: torch.Tensor | None   # which cmp_index entries take part
+    ori_valid: torch.Tensor | None = None   # which ori_index entries take part
+    ori_explicit: bool = False       # ori_index holds physical slots
 
 
 def select(case, batch: int, token: int) -> Selection:
-    """Row selection of reference.py:224-253 for the paths this build covers
-    (no explicit original slots, query_group == 1)."""
+    """Row selection of reference.py:224-253 for query_group == 1: the window, or the caller's own
+    physical slots of the original cache (:235-239; holes keep their place and are masked)."""
     first, last = int(case.cu_q[batch]), int(case.cu_q[batch + 1])
     length = int(case.seq_lens[batch])
     position = length - last + token
-    ori = torch.arange(max(0, position + 1 - case.window), position + 1)
+    explicit = getattr(case, "ori_indices", None) is not None
+    if explicit:
+        ori = case.ori_indices[token, 0].long()
+        ori_valid = (ori >= 0) & (ori < case.ori.shape[0] * case.ori.shape[1])
+    else:
+        ori = torch.arange(max(0, position + 1 - case.window), position + 1)
+        ori_valid = torch.ones_like(ori, dtype=torch.bool)
     cmp_index = cmp_valid = None
     if case.ratio != 1:
         count = (position + 1) // case.ratio
@@ -119,7 +133,7 @@ def select(case, batch: int, token: int) -> Selection:
             # short contexts: the valid entries are packed to the front, order kept
             cmp_index = cmp_index[cmp_valid]
             cmp_valid = torch.ones_like(cmp_index, dtype=torch.bool)
-    return Selection(token, batch, position, ori, cmp_index, cmp_valid)
+    return Selection(token, batch, position, ori, cmp_index, cmp_valid, ori_valid, explicit)
 
 
 def tokens_of(case):
@@ -193,8 +207,7 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
     outputs, lses = [], []
     for batch, token in tokens_of(case):
         sel = select(case, batch, token)
-        groups = [(case.ori, case.ori_block_table, sel.ori_index,
-                   torch.ones_like(sel.ori_index, dtype=torch.bool), ori_scale)]
+        groups = [(case.ori, case.ori_block_table, sel.ori_index, sel.ori_valid, ori_scale)]
         if case.ratio != 1:
             groups.append((case.cmp, case.cmp_block_table, sel.cmp_index, sel.cmp_valid, cmp_scale))
         deal = tile_parts[token] if tile_parts is not None else None
@@ -214,7 +227,8 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
                 tile_number += 1
                 ix, keep = index[start:start + tile_size], valid[start:start + tile_size]
                 kv = torch.zeros((ix.numel(), DIM), dtype=torch.int32)
-                kv[keep] = _paged_rows(cache, table, batch, ix[keep]).int()
+                kv[keep] = (_slot_rows(cache, ix[keep]) if kind == 0 and sel.ori_explicit
+                            else _paged_rows(cache, table, batch, ix[keep])).int()
                 qk_hi, qk_lo = q_hi @ kv.T, q_lo @ kv.T
                 dots = qk_hi.float()
                 dots += qk_lo.float() * INV127
@@ -286,8 +300,12 @@ def attention_float64(case, ori_scale=None, cmp_scale=None):
     for batch, token in tokens_of(case):
         first, last = int(case.cu_q[batch]), int(case.cu_q[batch + 1])
         position = int(case.seq_lens[batch]) - last + token
-        ori_ix = torch.arange(max(0, position - case.window + 1), position + 1)
-        rows = _paged_rows(case.ori, case.ori_block_table, batch, ori_ix)
+        if getattr(case, "ori_indices", None) is not None:
+            slots = case.ori_indices[token, 0].long()
+            rows = _slot_rows(case.ori, slots[(slots >= 0) & (slots < case.ori.shape[0] * case.ori.shape[1])])
+        else:
+            ori_ix = torch.arange(max(0, position - case.window + 1), position + 1)
+            rows = _paged_rows(case.ori, case.ori_block_table, batch, ori_ix)
         rows = (dequantize_rows(rows, ori_scale) if ori_scale is not None else rows).double()
         if case.ratio != 1:
             count = (position + 1) // case.ratio

@@ -33,7 +33,12 @@ int main(int argc, char **argv)
     auto uniform = [&](uint32_t lo, uint32_t hi) { return lo + (uint32_t)(rng() % (hi - lo + 1)); };
     unsigned long long pieces_seen = 0, split_tokens = 0;
     for (unsigned trial = 0; trial < workloads; ++trial) {
-        const uint32_t ratio = (rng() & 1) ? 4u : 128u;
+        const uint32_t kinds[4] = {4u, 128u, 128u, 1u};
+        const uint32_t ratio = kinds[rng() % 4];
+        // explicit original slots (always for ratio 1 here, sometimes for the others): several original tiles
+        const bool explicit_slots = ratio == 1 ? rng() % 4 != 0 : rng() % 8 == 0;
+        const uint32_t ori_tiles = original_tiles(explicit_slots, uniform(1, 2048));
+
         const uint32_t grid = trial % 7 == 0 ? uniform(1, 4) : uniform(1, kMaxCtas);
         // batch sizes: mostly serving-sized, sometimes very large, sometimes tiny
         const uint32_t shape = rng() % 10;
@@ -71,11 +76,13 @@ int main(int argc, char **argv)
             for (int32_t t = cu[b]; t < cu[b + 1]; ++t) {
                 const int32_t position = token_position(seq[b], cu[b + 1], (uint32_t)t);
                 REQUIRE(position >= 0 && position < seq[b]);
-                tiles[t] = tiles_of_token(ratio, position, topk);
+                tiles[t] = tiles_of_token(ratio, position, topk, ori_tiles);
                 const uint32_t rows = (uint32_t)(position + 1) / ratio;
-                REQUIRE(tiles[t] >= 1);
-                if (ratio == 128) REQUIRE((tiles[t] - 1) * kTileKeys >= rows && (tiles[t] - 1) * kTileKeys < rows + kTileKeys);
-                if (ratio == 4) REQUIRE(tiles[t] == 1 + (rows ? (topk + 127) / 128 : 0));
+                REQUIRE(tiles[t] >= ori_tiles && ori_tiles >= 1 && (explicit_slots || ori_tiles == 1));
+                const uint32_t compressed = tiles[t] - ori_tiles;
+                if (ratio == 128) REQUIRE(compressed * kTileKeys >= rows && compressed * kTileKeys < rows + kTileKeys);
+                if (ratio == 4) REQUIRE(compressed == (rows ? (topk + 127) / 128 : 0));
+                if (ratio == 1) REQUIRE(compressed == 0);
                 total_tiles += tiles[t];
             }
         const uint32_t cost = total_cost(total_tiles, live_tokens);

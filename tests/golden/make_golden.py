@@ -160,16 +160,56 @@ def layout_golden(reference):
     print('cache_layout', {k: v.get('stride') for k, v in result.items()}, flush=True)
 
 
+def slots_golden(ref):
+    """slots_swa.npz / slots_c4.npz: explicit original slots through the reference's tiled oracle."""
+    # ---- explicit original slots (reference.py:235-239): a ratio-1 layer as the draft model's
+    #      attention uses it (no compressed cache, 300 physical slots per token with holes, out-of-range
+    #      entries and duplicates), and a C4 layer with 160 slots in place of the window
+    def slot_case(ratio, queries, lengths, slots_per_token, seed):
+        case, oq, cq = windowed_case(ref, ratio=max(ratio, 4), queries=queries, lengths=lengths, seed=seed)
+        g = torch.Generator().manual_seed(seed + 100)
+        total = case.ori.shape[0] * 32
+        slots = torch.randint(0, total, (sum(queries), 1, slots_per_token), generator=g, dtype=torch.int32)
+        slots[:, :, ::9] = -1
+        slots[:, :, 4::17] = total + 5
+        slots[0, 0, 10:20] = slots[0, 0, 30:40]
+        if ratio == 1:
+            case = replace(case, cmp=None, cmp_block_table=None, cmp_indices=None, ratio=1)
+        return replace(case, ori_indices=slots), oq, cq
+
+    def save_slot_case(name, case, oq, cq):
+        arrays = dict(q=bits(case.q), ori=case.ori.numpy(), ori_table=case.ori_block_table.numpy(), cu_q=case.cu_q.numpy(),
+                      seq_lens=case.seq_lens.numpy(), sink=case.sink.numpy(), ori_scale=oq.scale.numpy(),
+                      ratio=np.int32(case.ratio), softmax_scale=np.float64(case.softmax_scale), ori_indices=case.ori_indices.numpy())
+        if case.ratio != 1:
+            arrays.update(cmp=case.cmp.numpy(), cmp_table=case.cmp_block_table.numpy(), cmp_scale=cq.scale.numpy(),
+                          cmp_indices=case.cmp_indices.numpy())
+        for splits in (1, 2):
+            out, lse = ref.tiled_quantized_reference(case, oq, cq if case.ratio != 1 else None, tile_size=128, splits=splits,
+                                                     return_lse=True)
+            arrays[f'out_s{splits}'] = bits(out)
+            arrays[f'lse_s{splits}'] = lse.numpy()
+        np.savez_compressed(HERE / f'{name}.npz', **arrays)
+        print(name, {k: v.shape for k, v in arrays.items() if hasattr(v, 'shape') and v.ndim}, flush=True)
+
+    save_slot_case('slots_swa', *slot_case(1, [2, 1, 3], [900, 4100, 37], 300, seed=21))
+    save_slot_case('slots_c4', *slot_case(4, [1, 2], [4200, 1500], 160, seed=22))
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument('--reference', type=Path, required=True, help='checkout of the reference project')
     parser.add_argument('--only-layout', action='store_true', help='regenerate cache_layout.json alone (needs vllm)')
+    parser.add_argument('--only-slots', action='store_true', help='regenerate the explicit-slot cases alone')
     args = parser.parse_args()
     if args.only_layout:
         layout_golden(args.reference)
         return
     sys.path.insert(0, str(args.reference))
     from npu_sparse_attn_sharedkv_int8 import reference as ref
+    if args.only_slots:
+        slots_golden(ref)
+        return
     from tests.support.serving_shapes import ActivationCorpus, Geometry
 
     # ---- writer: known answers and a random block (reference tests/unit/test_reference.py:22-27)
@@ -240,6 +280,8 @@ def main():
                        ori_block_table=source.ori_block_table[:, :math.ceil(max(lengths) / 32)].contiguous(),
                        cmp_block_table=source.cmp_block_table[:, :max(1, math.ceil(max(lengths) / (ratio * 32)))].contiguous())
         save_case(f'real_c{ratio}', case, oq, cq, ref)
+
+    slots_golden(ref)
 
     layout_golden(args.reference)
 

@@ -9,6 +9,7 @@ from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, SharedKVC
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 ATTENTION_CASES = ("unit_c4", "unit_c128", "config0_c4", "holes_c4", "short_c4", "mixed_c128", "real_c4", "real_c128")
+SLOT_CASES = ("slots_swa", "slots_c4")       # explicit original slots: a ratio-1 layer and a C4 layer
 PAGE_STRIDE = 622592          # the non-unit page stride the reference's device tests use (tests/support/serving_shapes.py:19)
 
 
@@ -20,12 +21,12 @@ def load_case(name):
     """Returns (case, ori_scale, cmp_scale, arrays) for a golden attention case."""
     z = np.load(GOLDEN / f"{name}.npz")
     t = lambda key: torch.from_numpy(z[key].copy())
+    optional = lambda key: t(key) if key in z else None
     case = SharedKVCase(
         q=bf16(z["q"]), ori=t("ori"), ori_block_table=t("ori_table"), cu_q=t("cu_q"), seq_lens=t("seq_lens"),
-        sink=t("sink"), cmp=t("cmp"), cmp_block_table=t("cmp_table"),
-        cmp_indices=t("cmp_indices") if "cmp_indices" in z else None,
-        ratio=int(z["ratio"]), softmax_scale=float(z["softmax_scale"]))
-    return case, t("ori_scale"), t("cmp_scale"), z
+        sink=t("sink"), cmp=optional("cmp"), cmp_block_table=optional("cmp_table"), cmp_indices=optional("cmp_indices"),
+        ratio=int(z["ratio"]), softmax_scale=float(z["softmax_scale"]), ori_indices=optional("ori_indices"))
+    return case, t("ori_scale"), optional("cmp_scale"), z
 
 
 def strided_pages(cache, device, stride=PAGE_STRIDE, offset=0):
@@ -42,7 +43,7 @@ def to_device(case, device, *, stride=None, offset=0):
     dev = case.to(device)
     if stride is not None:
         dev = replace(dev, ori=strided_pages(case.ori, device, stride, offset),
-                      cmp=strided_pages(case.cmp, device, stride, offset))
+                      cmp=strided_pages(case.cmp, device, stride, offset) if case.cmp is not None else None)
     return dev
 
 
@@ -66,15 +67,19 @@ def device_tile_parts(case, ctas):
     token with at least one compressed row has 1 + ceil(topk / 128) tiles, a C128 token
     1 + ceil(rows / 128), a token that sees no compressed row has 1."""
     counts = []
+    slots = getattr(case, "ori_indices", None)
+    original = -(-slots.shape[-1] // 128) if slots is not None else 1      # explicit slots: one tile per 128 entries
     for batch in range(case.seq_lens.numel()):
         first, last = int(case.cu_q[batch]), int(case.cu_q[batch + 1])
         for token in range(first, last):
             position = int(case.seq_lens[batch]) - last + token
             rows = (position + 1) // case.ratio if position >= 0 else 0
-            if case.ratio == 4:
-                counts.append(1 + (-(-case.cmp_indices.shape[-1] // 128) if rows else 0))
+            if case.ratio == 1:
+                counts.append(original)
+            elif case.ratio == 4:
+                counts.append(original + (-(-case.cmp_indices.shape[-1] // 128) if rows else 0))
             else:
-                counts.append(1 + -(-rows // 128))
+                counts.append(original + -(-rows // 128))
     # ranges are cut in units of cost: a token's tiles plus ITEM_COST units in front of its first tile
     total = sum(counts) + ITEM_COST * len(counts)
     quota = max(1, -(-total // ctas))

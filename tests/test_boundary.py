@@ -58,6 +58,12 @@ def test_host_side_rejections_need_no_gpu():
     from npu_sparse_attn_sharedkv_int8.attention import _Args
     args = _Args(tokens=4, batch=1, heads=8, ratio=4, window=128, oriBlock=32, cmpBlock=32, topk=1024)
     assert lib.sharedkv_attention(ctypes.addressof(args), 0, 99, -1, null) == -2          # unknown variant
+    assert lib.launch_sharedkv(0, null, None) == -22
+    args.ratio = 2
+    assert lib.sharedkv_attention(ctypes.addressof(args), 0, 0, -1, null) == -22         # general entry: ratio 1, 4 or 128 only
+    args.ratio = 4
+    args.oriIndices = 4
+    assert lib.sharedkv_attention(ctypes.addressof(args), 0, 20, -1, null) == -22        # the C4 entry takes no explicit slots
     assert lib.sharedkv_attention(ctypes.addressof(args), 0, 20, -1, null) == -22         # null pointers
     assert b"variant" in lib.sharedkv_status_string(-2)
     assert b"invalid" in lib.sharedkv_status_string(-22)
@@ -77,9 +83,13 @@ def test_route_selector_and_abi_guard():
         c8_attention.enabled()
     valid = dict(heads=8, tokens=48, batch=8, ratio=4, window=128, oriBlock=32, cmpBlock=32, oriIndices=0, topk=1024)
     assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**valid)))
-    for key, value in (("tokens", 0), ("batch", 0), ("heads", 16), ("ratio", 1), ("window", 129), ("oriBlock", 64),
-                       ("cmpBlock", 64), ("oriIndices", 1), ("topk", 2048)):
+    for key, value in (("tokens", 0), ("batch", 0), ("heads", 16), ("ratio", 2), ("window", 129), ("oriBlock", 64),
+                       ("cmpBlock", 64), ("oriIndices", 1), ("topk", 2048)):       # explicit slots need oriTopk > 0
         assert not c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | {key: value}))))
+    # beyond the reference's C4 / C128 route (its general kernel's territory): the same CUDA kernels serve
+    # ratio-1 layers (no compressed cache, so its block size is not looked at) and explicit original slots
+    assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(ratio=1, cmpBlock=0, topk=0)))))
+    assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(oriIndices=1, oriTopk=300)))))
     for batch, tokens in ((9, 49), (23, 138), (128, 768), (1024, 8192)):
         assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(batch=batch, tokens=tokens)))))
     assert c8_attention.supported(SimpleNamespace(blocks=24, args=_Args(**(valid | dict(ratio=128, topk=0)))))

@@ -16,7 +16,7 @@ import pytest
 import torch
 
 from oracle import sharedkv_oracle as oracle
-from tests.support import (ATTENTION_CASES, PAGE_STRIDE, bf16, device_tile_parts, error_metrics, load_case,
+from tests.support import (ATTENTION_CASES, PAGE_STRIDE, SLOT_CASES, bf16, device_tile_parts, error_metrics, load_case,
                            to_device)
 
 pytestmark = pytest.mark.gpu
@@ -25,7 +25,7 @@ DEVICE = "cuda:0"
 
 def prepared(case, ori_scale, cmp_scale, **kw):
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
-    return PreparedAttention(case, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), **kw)
+    return PreparedAttention(case, ori_scale.to(DEVICE), None if cmp_scale is None else cmp_scale.to(DEVICE), **kw)
 
 
 def sm_count():
@@ -49,7 +49,7 @@ def check_against_reference(out, lse, z, case=None, scales=None, ctas=None):
     return m
 
 
-@pytest.mark.parametrize("name", ATTENTION_CASES)
+@pytest.mark.parametrize("name", ATTENTION_CASES + SLOT_CASES)
 def test_golden_cases(name):
     case, ori_scale, cmp_scale, z = load_case(name)
     op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
@@ -63,7 +63,7 @@ def test_golden_cases(name):
 
 
 @pytest.mark.parametrize("stride,offset", [(PAGE_STRIDE, 16384), (16384 + 48, 16)])
-@pytest.mark.parametrize("name", ("config0_c4", "mixed_c128", "real_c4"))
+@pytest.mark.parametrize("name", ("config0_c4", "mixed_c128", "real_c4", "slots_swa"))
 def test_page_stride_and_offset_views(name, stride, offset):
     """Compact-layout views (whole-row strides: TMA row gather) and strides that are not a
     multiple of 512 bytes (cp.async row gather)."""
@@ -103,7 +103,8 @@ def run_debug(op, max_tiles, ctas=0):
 
 @pytest.mark.parametrize("legacy_gather", [False, True])
 @pytest.mark.parametrize("name,ctas", [("config0_c4", 1), ("holes_c4", 1), ("short_c4", 1), ("mixed_c128", 1),
-                                       ("real_c128", 1), ("config0_c4", 0), ("mixed_c128", 0), ("short_c4", 5)])
+                                       ("real_c128", 1), ("config0_c4", 0), ("mixed_c128", 0), ("short_c4", 5),
+                                       ("slots_swa", 1), ("slots_swa", 0), ("slots_c4", 1), ("slots_c4", 3)])
 def test_integer_stages_are_exact(name, ctas, legacy_gather):
     case, ori_scale, cmp_scale, z = load_case(name)
     trace = oracle.Trace()
@@ -155,7 +156,7 @@ def test_integer_stages_are_exact(name, ctas, legacy_gather):
         assert p_differs <= max(2, p_total // 200), (p_differs, p_total)
 
 
-@pytest.mark.parametrize("name", ATTENTION_CASES)
+@pytest.mark.parametrize("name", ATTENTION_CASES + SLOT_CASES)
 def test_production_kernel_gives_the_bits_of_the_instrumented_kernel(name):
     """The integer-stage proofs above run the kernel instantiation that dumps its intermediates;
     the instantiation that serving and the benchmark launch is another binary.  Same grid, same
@@ -241,8 +242,10 @@ def test_contract_violations():
         PreparedAttention(dev, *scales, implementation="fallback")
     with pytest.raises(ValueError):
         PreparedAttention(dev, *scales, tile_size=512)
+    with pytest.raises(ValueError):                                      # explicit slots: INT32 [T, 1, K] on the query device
+        PreparedAttention(replace(dev, ori_indices=torch.zeros((dev.q.shape[0], 1, 8), dtype=torch.int64, device=DEVICE)), *scales)
     with pytest.raises(ValueError):
-        PreparedAttention(replace(dev, ori_indices=torch.zeros((3, 1, 8), dtype=torch.int32, device=DEVICE)), *scales)
+        PreparedAttention(replace(dev, ori_indices=torch.zeros((dev.q.shape[0], 8), dtype=torch.int32, device=DEVICE)), *scales)
     empty = replace(dev, q=dev.q[:0], cmp_indices=dev.cmp_indices[:0])
     op = PreparedAttention(empty, *scales)
     assert op.blocks == 0 and op.run().shape == (0, 8, 512)

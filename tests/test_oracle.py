@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import sharedkv_oracle as oracle
-from tests.support import ATTENTION_CASES, GOLDEN, bf16, load_case
+from tests.support import ATTENTION_CASES, SLOT_CASES, GOLDEN, bf16, load_case
 
 
 def test_rounding_and_clipping_known_answer():
@@ -66,6 +66,18 @@ def test_joint_softmax_known_answer_and_random_row():
 def test_tiled_attention_reproduces_reference_bit_for_bit(name):
     case, ori_scale, cmp_scale, z = load_case(name)
     for splits in (1, 2, 3):
+        out, lse = oracle.attention_tiled(case, ori_scale, cmp_scale, tile_size=128, splits=splits, return_lse=True)
+        assert torch.equal(out, bf16(z[f"out_s{splits}"])), (name, splits)
+        assert torch.equal(lse, torch.from_numpy(z[f"lse_s{splits}"])), (name, splits)
+
+
+@pytest.mark.parametrize("name", SLOT_CASES)
+def test_explicit_original_slots_reproduce_reference_bit_for_bit(name):
+    """reference.py:235-239,285: the caller names the original rows by physical slot; negative and
+    out-of-range entries are masked in place, duplicates count twice; ratio 1 has no compressed kind."""
+    case, ori_scale, cmp_scale, z = load_case(name)
+    assert case.ori_indices is not None and (case.ratio == 1) == (case.cmp is None)
+    for splits in (1, 2):
         out, lse = oracle.attention_tiled(case, ori_scale, cmp_scale, tile_size=128, splits=splits, return_lse=True)
         assert torch.equal(out, bf16(z[f"out_s{splits}"])), (name, splits)
         assert torch.equal(lse, torch.from_numpy(z[f"lse_s{splits}"])), (name, splits)
