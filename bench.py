@@ -55,7 +55,7 @@ ROW_BYTES = 512
 # DRAM traffic (read + written) per algorithmic KV byte, from profiler captures of smaller launches
 # of the same kernels (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of
 # the captured launch); traffic grows in proportion to the queries processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.076, 128: 1.040}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.078, 128: 1.040}
 
 
 def measured_peaks():
@@ -107,7 +107,7 @@ def pair_bytes(lengths):
 
 def workload_label(args):
     return {"box": f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128",
-            "c128": "C128 decode, B=64, T=1, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)",
+            "c128": f"C128 decode, B=64, T={args.queries}, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)",
             "c4mtp": "C4 decode with MTP, B=256, T=2, ctx U[32k,128k], top-k 1024 + window 128",
             "writer": "paged INT8 cache writer: 65536 BF16 rows -> original cache + 16384 rows -> ratio-4 compressed cache, random slots"
             }[args.workload]
@@ -130,7 +130,7 @@ def build_workload(args, rank, world):
     elif args.workload == "c128":
         lengths = synthetic.uniform_lengths(64, 8192, 131072, seed=1)
         ratios = [128] * args.rotate
-        work = synthetic.build("c128", device, lengths, ratios=ratios, queries=1, seed=200 + rank, stride_slots=38,
+        work = synthetic.build("c128", device, lengths, ratios=ratios, queries=args.queries, seed=200 + rank, stride_slots=38,
                                slot_offset=1, max_context=135000)
     else:
         lengths = synthetic.uniform_lengths(256, 32768, 131072, seed=2)
@@ -625,6 +625,7 @@ def main():
     parser.add_argument("--layers", default="pair", choices=("pair", "c4", "c128"),
                         help="box workload: layer kinds per pair (one kind keeps a profiler capture small)")
     parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
+    parser.add_argument("--queries", type=int, default=1, help="query tokens per request of the c128 workload (chunked-prefill shapes)")
     parser.add_argument("--passes", type=int, default=0,
                         help="decode passes per step; 0 = as many as make the timed steps last --seconds")
     parser.add_argument("--seconds", type=float, default=2.5, help="length aimed at for the timed region when --passes is 0")

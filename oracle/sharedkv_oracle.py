@@ -106,34 +106,51 @@ class Selection:
     cmp_valid: torch.Tensor | None   # which cmp_index entries take part
     ori_valid: torch.Tensor | None = None   # which ori_index entries take part
     ori_explicit: bool = False       # ori_index holds physical slots
+    cmp_bias: torch.Tensor | None = None    # log(multiplicity) per cmp_index entry (grouped C4 only)
 
 
-def select(case, batch: int, token: int) -> Selection:
-    """Row selection of reference.py:224-253 for query_group == 1: the window, or the caller's own
-    physical slots of the original cache (:235-239; holes keep their place and are masked)."""
+def select(case, batch: int, token: int, query_group: int = 1) -> Selection:
+    """Row selection of reference.py:224-253: the window, or the caller's own physical slots of the
+    original cache (:235-239; holes keep their place and are masked).
+
+    With query_group > 1 (:229-234, 243-249) adjacent query tokens of a request share their tiles:
+    the original rows are the union of the group's windows, tiled from the union's first row, with the
+    token's own window as validity; a C128 token walks the prefix of the group's last token; a C4
+    token walks ALL compressed rows of the group's last token, each weighted by how often its own
+    top-k list names it (a bias of log(multiplicity) on the logit), rows it does not name masked."""
     first, last = int(case.cu_q[batch]), int(case.cu_q[batch + 1])
     length = int(case.seq_lens[batch])
     position = length - last + token
+    group_first = first + (token - first) // query_group * query_group
+    group_last = min(last, group_first + query_group) - 1
+    first_pos, last_pos = length - last + group_first, length - last + group_last
     explicit = getattr(case, "ori_indices", None) is not None
     if explicit:
+        if query_group != 1:
+            raise ValueError("Explicit original slots require ungrouped queries")
         ori = case.ori_indices[token, 0].long()
         ori_valid = (ori >= 0) & (ori < case.ori.shape[0] * case.ori.shape[1])
     else:
-        ori = torch.arange(max(0, position + 1 - case.window), position + 1)
-        ori_valid = torch.ones_like(ori, dtype=torch.bool)
-    cmp_index = cmp_valid = None
+        ori = torch.arange(max(0, first_pos + 1 - case.window), last_pos + 1)
+        ori_valid = (ori >= max(0, position + 1 - case.window)) & (ori <= position)
+    cmp_index = cmp_valid = cmp_bias = None
     if case.ratio != 1:
         count = (position + 1) // case.ratio
         if case.ratio == 4:
             cmp_index = case.cmp_indices[token, 0].long()
         else:
-            cmp_index = torch.arange(count)
+            cmp_index = torch.arange((last_pos + 1) // case.ratio)
         cmp_valid = (cmp_index >= 0) & (cmp_index < count)
-        if case.ratio == 4 and count < cmp_index.numel() <= 1024:
+        if case.ratio == 4 and query_group > 1:
+            multiplicity = torch.bincount(cmp_index[cmp_valid], minlength=(last_pos + 1) // 4).float()
+            cmp_index = torch.arange(multiplicity.numel())
+            cmp_valid = multiplicity > 0
+            cmp_bias = multiplicity.clamp_min(1).log()
+        elif case.ratio == 4 and count < cmp_index.numel() <= 1024:
             # short contexts: the valid entries are packed to the front, order kept
             cmp_index = cmp_index[cmp_valid]
             cmp_valid = torch.ones_like(cmp_index, dtype=torch.bool)
-    return Selection(token, batch, position, ori, cmp_index, cmp_valid, ori_valid, explicit)
+    return Selection(token, batch, position, ori, cmp_index, cmp_valid, ori_valid, explicit, cmp_bias)
 
 
 def tokens_of(case):
@@ -190,7 +207,7 @@ class Trace:
     tiles: list = field(default_factory=list)
 
 
-def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
+def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1, query_group=1,
                     return_lse=False, trace: Trace | None = None, tile_parts=None):
     """Online-softmax INT8 attention, tile by tile   (reference.py:210-323).
 
@@ -206,7 +223,7 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
     heads = case.q.shape[1]
     outputs, lses = [], []
     for batch, token in tokens_of(case):
-        sel = select(case, batch, token)
+        sel = select(case, batch, token, query_group)
         groups = [(case.ori, case.ori_block_table, sel.ori_index, sel.ori_valid, ori_scale)]
         if case.ratio != 1:
             groups.append((case.cmp, case.cmp_block_table, sel.cmp_index, sel.cmp_valid, cmp_scale))
@@ -233,6 +250,8 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
                 dots = qk_hi.float()
                 dots += qk_lo.float() * INV127
                 logits = dots * (alpha[:, None] * case.softmax_scale)
+                if kind == 1 and sel.cmp_bias is not None:
+                    logits += sel.cmp_bias[ix]                      # duplicate selections count as often as they are named
                 logits[:, ~keep] = MASKED
                 new_max = torch.maximum(maximum[part], logits.amax(-1))
                 rescale = torch.exp(maximum[part] - new_max)

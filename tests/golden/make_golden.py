@@ -196,11 +196,36 @@ def slots_golden(ref):
     save_slot_case('slots_c4', *slot_case(4, [1, 2], [4200, 1500], 160, seed=22))
 
 
+def grouped_golden(ref):
+    """grouped_c128.npz / grouped_c4.npz: `tiled_quantized_reference(..., query_group=2 / 4)` on chunked-prefill
+    shapes (several query tokens per request), reference.py:229-234,243-249,300-301."""
+    for name, ratio, queries, lengths, seed in (('grouped_c128', 128, [5, 2, 1], [16500, 40000, 300], 31),
+                                                ('grouped_c4', 4, [4, 3], [700, 2051], 32)):
+        def duplicate(indices, g):
+            indices[:, :, 40:60] = indices[:, :, 0:20]             # duplicates: multiplicity 2
+        case, oq, cq = windowed_case(ref, ratio=ratio, queries=queries, lengths=lengths, seed=seed,
+                                     edit_indices=duplicate if ratio == 4 else None)
+        arrays = dict(q=bits(case.q), ori=case.ori.numpy(), ori_table=case.ori_block_table.numpy(), cmp=case.cmp.numpy(),
+                      cmp_table=case.cmp_block_table.numpy(), cu_q=case.cu_q.numpy(), seq_lens=case.seq_lens.numpy(),
+                      sink=case.sink.numpy(), ori_scale=oq.scale.numpy(), cmp_scale=cq.scale.numpy(),
+                      ratio=np.int32(case.ratio), softmax_scale=np.float64(case.softmax_scale))
+        if case.cmp_indices is not None:
+            arrays['cmp_indices'] = case.cmp_indices.numpy()
+        for group in (1, 2, 4):
+            out, lse = ref.tiled_quantized_reference(case, oq, cq, tile_size=128, splits=1, query_group=group, return_lse=True)
+            arrays[f'out_g{group}'] = bits(out)
+            arrays[f'lse_g{group}'] = lse.numpy()
+        arrays['out_s1'], arrays['lse_s1'] = arrays['out_g1'], arrays['lse_g1']
+        np.savez_compressed(HERE / f'{name}.npz', **arrays)
+        print(name, {k: v.shape for k, v in arrays.items() if hasattr(v, 'shape') and v.ndim}, flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument('--reference', type=Path, required=True, help='checkout of the reference project')
     parser.add_argument('--only-layout', action='store_true', help='regenerate cache_layout.json alone (needs vllm)')
     parser.add_argument('--only-slots', action='store_true', help='regenerate the explicit-slot cases alone')
+    parser.add_argument('--only-grouped', action='store_true', help='regenerate the query-group cases alone')
     args = parser.parse_args()
     if args.only_layout:
         layout_golden(args.reference)
@@ -209,6 +234,9 @@ def main():
     from npu_sparse_attn_sharedkv_int8 import reference as ref
     if args.only_slots:
         slots_golden(ref)
+        return
+    if args.only_grouped:
+        grouped_golden(ref)
         return
     from tests.support.serving_shapes import ActivationCorpus, Geometry
 
@@ -282,6 +310,7 @@ def main():
         save_case(f'real_c{ratio}', case, oq, cq, ref)
 
     slots_golden(ref)
+    grouped_golden(ref)
 
     layout_golden(args.reference)
 

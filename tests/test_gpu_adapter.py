@@ -149,6 +149,31 @@ def test_layer_runtime_writes_attends_and_replays(adapter, ratio):
     assert all(op.case is None and op.out is None for op in state.attention_ops.values())
 
 
+def test_explicit_original_slots_through_the_adapter(adapter):
+    """The serving stack's draft layers name their original rows by physical slot
+    (`ori_sparse_indices`, vllm_adapter.py:154 of the reference): the adapter hands them to the kernels
+    through the general launcher; holes and out-of-range slots are masked."""
+    state, dev, writes, _, quantized, scales, source = build(adapter, 4)
+    for w in writes:
+        state.write(*w)
+    g = torch.Generator().manual_seed(41)
+    total = quantized.ori.shape[0] * 32
+    slots = torch.randint(0, total, (dev.q.shape[0], 1, 200), generator=g, dtype=torch.int32)
+    slots[:, :, ::7] = -1
+    slots[:, :, 3::11] = total + 1
+    out, lse = state.attention(dev.q, **{**call(dev, 4), "ori_sparse_indices": slots.to(DEVICE)})
+    torch.cuda.synchronize()
+    case = replace(quantized, ori_indices=slots)
+    ctas = min(torch.cuda.get_device_properties(0).multi_processor_count, 160)
+    want, want_lse = oracle.attention_tiled(case, scales[0].scale, scales[1].scale, return_lse=True,
+                                            tile_parts=device_tile_parts(case, ctas))
+    torch.testing.assert_close(out.cpu().float(), want.float(), rtol=0.008, atol=0.0003)
+    torch.testing.assert_close(lse.cpu().squeeze(-1), want_lse, rtol=2e-5, atol=2e-5)
+    plain, _ = oracle.attention_tiled(case, scales[0].scale, scales[1].scale, return_lse=True)
+    m = error_metrics(out.cpu().float(), plain.float())
+    assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+
+
 def test_operator_cache_is_bounded_and_calls_are_validated(adapter):
     vllm_adapter = adapter[0]
     state, dev, writes, _, _, _, _ = build(adapter, 4, batch=1, queries=1, length=300)

@@ -16,7 +16,7 @@ import pytest
 import torch
 
 from oracle import sharedkv_oracle as oracle
-from tests.support import (ATTENTION_CASES, PAGE_STRIDE, SLOT_CASES, bf16, device_tile_parts, error_metrics, load_case,
+from tests.support import (ATTENTION_CASES, GROUPED_CASES, PAGE_STRIDE, SLOT_CASES, bf16, device_tile_parts, error_metrics, load_case,
                            to_device)
 
 pytestmark = pytest.mark.gpu
@@ -60,6 +60,23 @@ def test_golden_cases(name):
     again = op.run().clone()
     torch.cuda.synchronize()
     assert torch.equal(again, out)                      # deterministic across launches
+
+
+@pytest.mark.parametrize("name", GROUPED_CASES)
+def test_chunked_prefill_shapes_against_the_grouped_reference(name):
+    """Several query tokens per request.  The kernel walks every token by itself (the arithmetic of
+    query_group = 1: bit-level bands against that reference output); the reference's grouped plans
+    (query_group 2 and 4, which share tiles between adjacent tokens and re-tile the window union)
+    attend the same keys, so their outputs are matched inside the acceptance band too."""
+    case, ori_scale, cmp_scale, z = load_case(name)
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, return_lse=True)
+    out = op.run()
+    torch.cuda.synchronize()
+    check_against_reference(out.cpu(), op.lse.cpu(), z, case, (ori_scale, cmp_scale))
+    for group in (2, 4):
+        m = error_metrics(out.cpu().float(), bf16(z[f"out_g{group}"]).float())
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, (group, m)
+        torch.testing.assert_close(op.lse.cpu(), torch.from_numpy(z[f"lse_g{group}"]), rtol=1e-4, atol=1e-4)
 
 
 @pytest.mark.parametrize("stride,offset", [(PAGE_STRIDE, 16384), (16384 + 48, 16)])

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import sharedkv_oracle as oracle
-from tests.support import ATTENTION_CASES, SLOT_CASES, GOLDEN, bf16, load_case
+from tests.support import ATTENTION_CASES, GROUPED_CASES, SLOT_CASES, GOLDEN, bf16, load_case
 
 
 def test_rounding_and_clipping_known_answer():
@@ -69,6 +69,22 @@ def test_tiled_attention_reproduces_reference_bit_for_bit(name):
         out, lse = oracle.attention_tiled(case, ori_scale, cmp_scale, tile_size=128, splits=splits, return_lse=True)
         assert torch.equal(out, bf16(z[f"out_s{splits}"])), (name, splits)
         assert torch.equal(lse, torch.from_numpy(z[f"lse_s{splits}"])), (name, splits)
+
+
+@pytest.mark.parametrize("name", GROUPED_CASES)
+def test_query_groups_reproduce_reference_bit_for_bit(name):
+    """reference.py:229-234,243-249,300-301: adjacent query tokens of a request share the union of their
+    windows and (C128) the longest prefix; a grouped C4 token walks every compressed row with a
+    log(multiplicity) bias for the rows its top-k list names, duplicates included."""
+    case, ori_scale, cmp_scale, z = load_case(name)
+    for group in (1, 2, 4):
+        out, lse = oracle.attention_tiled(case, ori_scale, cmp_scale, tile_size=128, query_group=group, return_lse=True)
+        assert torch.equal(out, bf16(z[f"out_g{group}"])), (name, group)
+        assert torch.equal(lse, torch.from_numpy(z[f"lse_g{group}"])), (name, group)
+    # grouping only re-tiles the same keys: the three results agree far inside the acceptance band
+    for group in (2, 4):
+        diff = (bf16(z[f"out_g{group}"]).float() - bf16(z["out_g1"]).float()).abs()
+        assert float(diff.max()) <= 2e-2 and float(diff.mean()) <= 2e-3
 
 
 @pytest.mark.parametrize("name", SLOT_CASES)
