@@ -795,8 +795,9 @@ def main():
                        "algorithmic_bytes_per_launch": rows * ROW_BYTES // launches, "launches": launches,
                        "timing": "CUDA events around replays of a graph holding this kind's launches back to back, after the sustained region"}
     dominant = max(per_kind, key=lambda r: per_kind[r][0])
-    cpu_qps, cpu_rows, cpu_n, cpu_kind = time_cpu_path(work.seq_lens_host, [l.ratio for l in work.layers], args.cpu_seconds,
-                                                       os.cpu_count() or 1)
+    # the CPU baseline is timed at N = 1 only (under torchrun the host's cores belong to all the ranks)
+    cpu_qps, cpu_rows, cpu_n, cpu_kind = time_cpu_path(work.seq_lens_host, [l.ratio for l in work.layers],
+                                                       args.cpu_seconds if world == 1 else 0.0, os.cpu_count() or 1)
     timed_s = total_ms / 1000
     line = {
         "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
