@@ -7,8 +7,10 @@
 // soon the memory system is full and how few dependent round trips a warp makes:
 //   * a warp's slots are read once, up front, one row per lane (a warp owns rows w, w + W, ...),
 //     and handed round by shuffles;
-//   * row loads do not wait for the slots: four rows per warp are requested unconditionally, and
+//   * row loads do not wait for the slots: two rows per warp are requested unconditionally, and
 //     only the store needs the slot (a row whose slot turns out to be invalid was read in vain);
+//     32 resident warps per SM keep 64 KB of reads in flight, more rows per warp only cost registers
+//     and residency (measured: 2 rows x 4 CTAs per SM 25.4 us per step, 4 x 3 26.8, 8 x 2 28.5);
 //   * the launch carries the programmatic-stream-serialization attribute, so its CTAs are resident
 //     and past their set-up when the previous kernel of the stream (often the other cache's
 //     writer) ends; nothing is read before griddepcontrol.wait returns.
@@ -35,8 +37,8 @@ using ptx::grid_dependency_launch_dependents;
 using ptx::grid_dependency_wait;
 
 constexpr int kWriterThreads = 256;          // 8 warps
-constexpr int kRowsInFlight = 4;             // rows a warp requests before it converts the first (divides 32)
-constexpr int kWriterCtasPerSm = 3;          // resident CTAs per SM the vector kernel is compiled for
+constexpr int kRowsInFlight = 2;             // rows a warp requests before it converts the first (divides 32)
+constexpr int kWriterCtasPerSm = 4;          // resident CTAs per SM the vector kernel is compiled for
 constexpr uint64_t kNoSlot = ~0ull;          // byte offset standing for "skip this row"
 
 __device__ __forceinline__ uint32_t quantize4(uint32_t lo2, uint32_t hi2, const float *inv)
