@@ -86,6 +86,10 @@ int launch_sharedkv(uint32_t, void *stream, const SharedKVArgs *args)
 {
     return sharedkv::attention(SHAREDKV_VARIANT_GENERAL, args, static_cast<cudaStream_t>(stream), nullptr);
 }
+int launch_sharedkv_paired(uint32_t, void *stream, const SharedKVArgs *args)
+{
+    return sharedkv::attention(SHAREDKV_VARIANT_PAIRED, args, static_cast<cudaStream_t>(stream), nullptr);
+}
 int launch_sharedkv_c8_sparse(uint32_t, void *stream, const SharedKVArgs *args)
 {
     return sharedkv::attention(SHAREDKV_VARIANT_C4, args, static_cast<cudaStream_t>(stream), nullptr);

@@ -1,5 +1,6 @@
 // INT8 shared-KV decode attention for sm_100a (C4: top-k compressed rows + window,
-// C128: every compressed row + window), eight heads, D = 512.
+// C128: every compressed row + window; ratio 1: the original cache only; optionally the caller's own
+// list of original slots in place of the window), eight heads, D = 512.
 //
 // One call = one kernel launch on the caller's stream (no memset, no second kernel): the split-K
 // tickets in the workspace are zero between launches because the CTA that merges a token puts its
@@ -50,7 +51,6 @@
 
 #include <atomic>
 #include <cstddef>
-#include <cstdlib>
 #include <cstring>
 
 #include "../../include/sharedkv_c_abi.h"
@@ -497,14 +497,57 @@ __device__ __noinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s
     return chunk * 32u + (bit & 31u);
 }
 
+// ------------------------------------------------------------------ grouped items (paired query tokens)
+// The paired kernel walks two adjacent query tokens of a request as ONE item whose tiles are
+// fetched once and visited by both tokens (reference.py:229-234,243-245 with query_group = 2): the
+// original rows are the union of the two windows, tiled from the union's first row; the compressed
+// rows are the prefix of the later token.  Such an item stores the position of its FIRST token and,
+// in bit 31 of `batch`, whether it holds a second one.
+constexpr uint32_t kPairBit = 0x80000000u;
+__device__ __forceinline__ uint32_t pair_tokens(uint32_t batch_word) { return (batch_word >> 31) + 1u; }
+__device__ __forceinline__ uint32_t pair_batch(uint32_t batch_word) { return batch_word & ~kPairBit; }
+// Position of the item's last token (negative: no token of the item sees a key).
+__device__ __forceinline__ int32_t pair_last_position(int32_t first_position, uint32_t tokens) { return first_position + (int32_t)tokens - 1; }
+__device__ __forceinline__ uint32_t pair_window_start(int32_t first_position)
+{
+    return first_position >= (int32_t)kWindow ? (uint32_t)first_position + 1u - kWindow : 0u;
+}
+// 128-key tiles of the window union of an item (1 or 2; 1 also when it has no row at all, so that
+// its output rows are written).
+__device__ __forceinline__ uint32_t pair_original_tiles(int32_t first_position, uint32_t tokens)
+{
+    const int32_t last = pair_last_position(first_position, tokens);
+    if (last < 0) return 1u;
+    const uint32_t rows = (uint32_t)last + 1u - pair_window_start(first_position);
+    return (rows + kTileKeys - 1u) / kTileKeys;
+}
+// Compressed rows an item walks: the prefix of its last token.
+__device__ __forceinline__ uint32_t pair_compressed_rows(int32_t first_position, uint32_t tokens)
+{
+    const int32_t last = pair_last_position(first_position, tokens);
+    return last < 0 ? 0u : ((uint32_t)last + 1u) / 128u;
+}
+
 // Stage A of the producer: candidate logical row of slot `slot` in the cursor's tile.
 // Values read from the top-k array are returned unchecked (stage B range-checks them, so
 // that the load is not consumed here); every other path returns a valid row or -1.
-template <int RATIO>
+template <int RATIO, bool GROUP>
 __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cursor &c, const Compaction &k, uint32_t slot,
                                                  uint32_t ori_tiles)
 {
     const Item &it = c.it;
+    if (GROUP) {
+        const uint32_t tokens = pair_tokens(it.batch);
+        const int32_t last = pair_last_position(it.position, tokens);
+        if (last < 0) return -1;
+        const uint32_t windows = pair_original_tiles(it.position, tokens);
+        if (c.j < windows) {
+            const uint32_t row = pair_window_start(it.position) + c.j * kTileKeys + slot;
+            return row <= (uint32_t)last ? (int32_t)row : -1;
+        }
+        const uint32_t s = (c.j - windows) * kTileKeys + slot;
+        return s < pair_compressed_rows(it.position, tokens) ? (int32_t)s : -1;
+    }
     if (it.position < 0) return -1;
     if (c.j < ori_tiles) {
         if (p.oriIndices) {
@@ -546,7 +589,7 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 constexpr int kLookahead = 1;
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
-template <int RATIO, bool TMA>
+template <int RATIO, bool TMA, bool GROUP>
 __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan,
                               uint32_t set, uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
                               const CUtensorMap *cmp_page_map)
@@ -606,9 +649,18 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             // ---- stage B: range check and page-table lookup for tile n - kLookahead
             int32_t off_b = -1, page_b = 0;
             if (n >= (uint32_t)kLookahead && !cb.done) {
-                const bool ori = cb.j < ori_tiles;
+                const bool ori = cb.j < (GROUP ? pair_original_tiles(cb.position, pair_tokens(cb.batch)) : ori_tiles);
                 const int32_t c = cand[u];
-                if (ori && explicit_slots) {
+                if (GROUP) {
+                    // the compressed prefix is that of the group's last token
+                    const uint32_t limit = ori ? 0x7fffffffu : pair_compressed_rows(cb.position, pair_tokens(cb.batch));
+                    const uint32_t request = pair_batch(cb.batch);
+                    if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
+                        off_b = (c & 31) | (ori ? 256 : 0);
+                        page_b = ori ? ori_table[(uint64_t)request * p.oriTableWidth + ((uint32_t)c >> 5)]
+                                     : cmp_table[(uint64_t)request * p.cmpTableWidth + ((uint32_t)c >> 5)];
+                    }
+                } else if (ori && explicit_slots) {
                     // a physical slot: page and row come from the value itself, no table is read
                     if (c >= 0 && ((uint32_t)c >> 5) < p.oriPages) { off_b = (c & 31) | 256; page_b = c >> 5; }
                 } else {
@@ -629,7 +681,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             // ---- stage A: candidate row for tile n
             int32_t cand_a = -1;
             if (!ca.done) {
-                cand_a = candidate_row<RATIO>(p, ca, comp, slot, ori_tiles);
+                cand_a = candidate_row<RATIO, GROUP>(p, ca, comp, slot, ori_tiles);
                 if (leader_advance(ca, items, plan, sm, set, 2) && RATIO == 4 && !ca.done) compaction_build(comp, p, ca.it, lane);
             }
             cand[u] = cand_a;
@@ -642,7 +694,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             const uint32_t t = 2u * issued + set;          // position of the tile in the CTA's sequence
             const uint32_t stage = t % kStages, pass = t / kStages;
             if (!wait_phase<2>(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
-            const bool ori = cc.j < ori_tiles;
+            const bool ori = cc.j < (GROUP ? pair_original_tiles(cc.position, pair_tokens(cc.batch)) : ori_tiles);
             const int32_t id = row_ring[u * 32];
             const bool valid = id != kRowsInMap;
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
@@ -1349,8 +1401,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
             tma_prefetch_descriptor(RATIO == 128 ? &cmp_page_map : &cmp_map);
         }
         const uint32_t set = warp >= kWarpProducerB ? 1u : 0u;
-        producer_loop<RATIO, TMA>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
-                                  &cmp_page_map);
+        producer_loop<RATIO, TMA, false>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
+                                         &cmp_page_map);
         cp_async_wait<0>();
     } else {
         if (kRegsIssue < kRegsLaunch) registers_release<kRegsIssue>();
@@ -1379,6 +1431,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
         tmem_dealloc(tmem, kTmemCols);
     }
 }
+
+#include "decode_paired.cuh"
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -1511,6 +1565,50 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
     return (int)e;
 }
 
+// Paired-query C128 launch (decode_paired.cuh): same grid, block and tensor maps as launch<128>.
+template <bool TMA>
+cudaError_t launch_decode_paired(const SharedKVArgs &a, const CUtensorMap &ori_map, const CUtensorMap &cmp_map,
+                                 const CUtensorMap &cmp_page_map, uint32_t grid, cudaStream_t stream, int device)
+{
+    static std::atomic<uint64_t> configured{0};
+    const bool cached = device >= 0 && device < kMaxDevices;
+    const uint64_t bit = cached ? 1ull << device : 0ull;
+    if (!cached || !(configured.load(std::memory_order_relaxed) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel_paired<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesPaired);
+        if (e != cudaSuccess) return e;
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kSmemBytesPaired;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = programmatic_launch_enabled() ? 1u : 0u;
+    return cudaLaunchKernelEx(&config, decode_kernel_paired<TMA>, a, ori_map, cmp_map, cmp_page_map);
+}
+
+int launch_paired(const SharedKVArgs &a, cudaStream_t stream, int sms)
+{
+    const uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    static const CUtensorMap no_map = {};
+    bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 &&
+               (uint64_t)a.oriPages * (a.oriStride / kDim) < (uint64_t)kRowsInMap && a.cmpStride / kDim < 65536;
+    const MapSet *maps = tma ? tensor_maps(a.ori, a.cmp, a.cmpStride, true) : nullptr;
+    if (maps == nullptr) tma = false;
+    const CUtensorMap &ori_map = tma ? maps->ori_map : no_map, &cmp_map = tma ? maps->cmp_map : no_map,
+                      &cmp_page_map = tma ? maps->cmp_page_map : no_map;
+    e = tma ? launch_decode_paired<true>(a, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+            : launch_decode_paired<false>(a, ori_map, cmp_map, cmp_page_map, grid, stream, device);
+    return (int)e;
+}
+
 }  // namespace
 
 int workspace_status(const void *workspace, cudaStream_t stream)
@@ -1527,14 +1625,16 @@ int workspace_status(const void *workspace, cudaStream_t stream)
 int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, const SharedKVDebug *debug)
 {
     if (args == nullptr) return SHAREDKV_EINVAL;
-    const bool general = variant == SHAREDKV_VARIANT_GENERAL;
-    if (!general && variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
+    const bool general = variant == SHAREDKV_VARIANT_GENERAL, paired = variant == SHAREDKV_VARIANT_PAIRED;
+    if (!general && !paired && variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
         return SHAREDKV_EVARIANT;
     SharedKVArgs a = *args;
     if (a.tokens == 0 || a.batch == 0) return SHAREDKV_OK;
     // The C4 / C128 entries take their own ratio and no explicit original slots, as the reference's
     // do; the general entry takes ratio 1 (no compressed cache), 4 or 128, with or without them.
-    const uint32_t ratio = general ? a.ratio : (variant == SHAREDKV_VARIANT_C128 ? 128u : 4u);
+    // The paired entry is the C128 arithmetic with two adjacent query tokens of a request per work item.
+    const uint32_t ratio = general ? a.ratio : ((variant == SHAREDKV_VARIANT_C128 || paired) ? 128u : 4u);
+    if (paired && (debug != nullptr || a.batch + 1u > kPlanStaged)) return SHAREDKV_EINVAL;
     if (a.ratio != ratio || (ratio != 1u && ratio != 4u && ratio != 128u) || (!general && a.oriIndices != 0)) return SHAREDKV_EINVAL;
     if (a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage) return SHAREDKV_EINVAL;
     if (a.oriIndices && (a.oriTopk == 0 || a.oriIndices % 4u)) return SHAREDKV_EINVAL;
@@ -1560,6 +1660,7 @@ int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, c
         return SHAREDKV_EINVAL;
     const int sms = device_sm_count();
     if (sms <= 0) return (int)cudaErrorInvalidDevice;
+    if (paired) return launch_paired(a, stream, sms);
     return ratio == 4 ? launch<4>(a, stream, debug, sms) : launch<128>(a, stream, debug, sms);
 }
 

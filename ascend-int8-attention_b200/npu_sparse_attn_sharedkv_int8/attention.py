@@ -100,17 +100,22 @@ class PreparedAttention:
         tokens, heads, device = _check_case(case, ori_scale, cmp_scale)
         self.case, self.scales = case, (ori_scale, cmp_scale)
         self._bind_outputs(output, lse_output, return_lse, tokens, heads, device)
-        # 128-key tiles, one query token per task, KV split on the device: the planning keywords of
-        # the reference are accepted only where they say the same
+        # 128-key tiles, KV split on the device: the planning keywords of the reference are accepted
+        # only where they say the same.  query_group = 2 (attention.py:96-100,189-190 of the reference)
+        # selects the paired-query C128 kernel: two adjacent tokens of a request share their tiles.
         _require(tile_size in (None, 128), "The CUDA kernels use 128-key tiles; tile_size must be None or 128")
-        _require(query_group in (None, 1), "The CUDA kernels process one query token per task; query_group must be None or 1")
+        _require(query_group in (None, 1, 2), "The CUDA kernels take one or two query tokens per task; query_group must be None, 1 or 2")
+        _require(query_group != 2 or (heads == 8 and case.ratio == 128),
+                 "Query grouping requires eight heads and a ratio-128 layer")
+        _require(query_group != 2 or case.ori_indices is None, "Explicit original slots require ungrouped queries")
         _require(splits is None or (isinstance(splits, int) and 1 <= splits <= 24), "Expected 1..24 KV partitions")
         _require(not (adaptive_splits or trim_cube_tails or dynamic_grouped_c128),
                  "Host-selected Ascend tile plans have no CUDA counterpart; leave them unset")
-        self.query_group, self.tile_size, self.splits = 1, 128, 1
+        self.query_group, self.tile_size, self.splits = query_group or 1, 128, 1
         self.adaptive_splits = self.trim_cube_tails = self.dynamic_grouped_c128 = False
         general = case.ratio == 1 or case.ori_indices is not None      # the reference's compatibility entry (variant 0)
-        self.dynamic_c4, self.dynamic_c128 = case.ratio == 4 and not general, case.ratio == 128 and not general
+        self.dynamic_c4 = case.ratio == 4 and not general
+        self.dynamic_c128 = case.ratio == 128 and not general and self.query_group == 1
         _require(max_seq_len is None or (isinstance(max_seq_len, int) and max_seq_len > 0
                                          and (case.ori_indices is not None
                                               or max_seq_len <= case.ori_block_table.shape[1] * case.ori.shape[1])

@@ -102,8 +102,9 @@ enum {
 };
 
 /* Kernel variants of the host bridge: 0 is the reference's general 128-key-tile kernel
- * (launch.cpp:33), 20-22 its C4 / C128 decode kernels (c8_launch.cpp:12-18). */
-enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
+ * (launch.cpp:33), 7 its paired-query C128 kernel (launch.cpp:40), 20-22 its C4 / C128 decode
+ * kernels (c8_launch.cpp:12-18). */
+enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_PAIRED = 7, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
 
 /* sizeof(SharedKVArgs) / sizeof(CacheWriteArgs) as compiled into the library; the
  * Python layer compares them with its ctypes mirrors (attention.py:223-226,
@@ -144,6 +145,14 @@ SHAREDKV_API int sharedkv_workspace_status(const void *workspace, void *stream);
  * the entries below.  Replaces csrc/kernels/sharedkv.cpp:585 (`launch_sharedkv`, variant 0 of
  * csrc/host/launch.cpp:33), the reference's kernel for everything outside its C4 / C128 route. */
 SHAREDKV_API int launch_sharedkv(uint32_t blocks, void *stream, const SharedKVArgs *args);
+
+/* Paired queries (ratio 128 only): two adjacent query tokens of a request are one work item whose
+ * keys are fetched once and used by both tokens, for launches with many query tokens per request
+ * (chunked prefill).  The results follow the reference's tiled arithmetic with query_group = 2
+ * (reference.py:229-234,243-245): the window rows of a pair are tiled from the first row of the
+ * union of the two windows.  No explicit original slots; batch < 11776.  Replaces
+ * csrc/kernels/sharedkv_paired.cpp:7 (`launch_sharedkv_paired`, variant 7 of launch.cpp:40). */
+SHAREDKV_API int launch_sharedkv_paired(uint32_t blocks, void *stream, const SharedKVArgs *args);
 
 /* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
  * query token.  `blocks` is accepted for signature compatibility and ignored: the

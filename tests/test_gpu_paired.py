@@ -1,0 +1,112 @@
+"""Paired-query C128 kernel (query_group = 2) on the GPU against the reference's grouped arithmetic.
+
+The reference's tiled oracle with query_group = 2 (reference.py:229-234,243-245) tiles the union of
+two adjacent tokens' windows from its first row and walks the later token's compressed prefix; the
+paired kernel follows that tiling and never splits an item, so its results are held to the
+reference's own device band (rtol 0.008, atol 0.0003 on BF16 output, 2e-5 on LSE; reference
+tests/npu/test_attention.py:102-103) against the golden `out_g2` and against the oracle.
+"""
+from dataclasses import replace
+import math
+
+import pytest
+import torch
+
+from oracle import sharedkv_oracle as oracle
+from tests.support import PAGE_STRIDE, bf16, error_metrics, load_case, strided_pages, to_device
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda:0"
+
+
+def prepared(case, ori_scale, cmp_scale, **kw):
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    return PreparedAttention(case, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2, return_lse=True, **kw)
+
+
+def assert_device_band(out, lse, expected, expected_lse):
+    torch.testing.assert_close(lse, expected_lse, rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(out.float(), expected.float(), rtol=0.008, atol=0.0003)
+
+
+def test_golden_grouped_case():
+    case, ori_scale, cmp_scale, z = load_case("grouped_c128")
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale)
+    assert op.variant == 7 and op.query_group == 2
+    op.workspace[1024:].fill_(0xA5)
+    out = op.run()
+    torch.cuda.synchronize()
+    from npu_sparse_attn_sharedkv_int8 import c8_attention
+    c8_attention.workspace_status(op)
+    assert_device_band(out.cpu(), op.lse.cpu(), bf16(z["out_g2"]), torch.from_numpy(z["lse_g2"]))
+    m = error_metrics(out.cpu().float(), bf16(z["out_g1"]).float())          # the same keys as the ungrouped walk
+    assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+    again = op.run().clone()
+    torch.cuda.synchronize()
+    assert torch.equal(again, out)
+
+
+def random_case(seed):
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    g = torch.Generator().manual_seed(7000 + seed)
+    pick = lambda options: options[int(torch.randint(len(options), (1,), generator=g))]
+    batch = int(torch.randint(1, 7, (1,), generator=g))
+    queries = [int(torch.randint(1, 10, (1,), generator=g)) for _ in range(batch)]
+    top = pick((70000, 40000, 9000, 300))
+    lengths = [max(q, int(math.exp(float(torch.rand(1, generator=g)) * math.log(top)))) for q in queries]
+    if seed % 4 == 0:
+        lengths[0] = queries[0]                       # positions 0 .. q - 1: windows shorter than a tile
+    if seed % 4 == 1:
+        lengths[-1] = 127 + queries[-1] // 2          # the window union crosses the 128-row mark inside the request
+    if seed % 4 == 2:
+        lengths[0] = 16384 + queries[0] // 2          # a compressed tile appears between the tokens of one request
+    source = make_case(query_lengths=tuple(queries), seq_lens=tuple(lengths), heads=8, ratio=128, topk=1024, seed=seed)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    stride = pick((16384, PAGE_STRIDE, 16384 + 512, 16384 + 48))
+    return case, oq.scale, cq.scale, stride, (16 if stride % 512 else 1024)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_geometry(seed):
+    case, ori_scale, cmp_scale, stride, offset = random_case(seed)
+    dev = case.to(DEVICE)
+    dev = replace(dev, ori=strided_pages(case.ori, DEVICE, stride, offset), cmp=strided_pages(case.cmp, DEVICE, stride, offset))
+    op = prepared(dev, ori_scale, cmp_scale)
+    out = op.run()
+    torch.cuda.synchronize()
+    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=2, return_lse=True)
+    assert_device_band(out.cpu(), op.lse.cpu(), expected, expected_lse)
+
+
+def test_chunked_prefill_chunk_with_a_dead_request():
+    """48 + 33 query tokens behind long contexts, then a request that is turned into padding after
+    the call was prepared (as a captured serving graph meets it): its rows come back as zeros."""
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    source = make_case(query_lengths=(48, 33, 7), seq_lens=(33000, 20000, 900), heads=8, ratio=128, topk=1024, seed=5)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    expected, expected_lse = oracle.attention_tiled(case, oq.scale, cq.scale, query_group=2, return_lse=True)
+    dev = case.to(DEVICE)
+    op = prepared(dev, oq.scale, cq.scale)
+    out = op.run()
+    torch.cuda.synchronize()
+    assert_device_band(out.cpu(), op.lse.cpu(), expected, expected_lse)
+    dev.seq_lens[2:] = 0
+    dev.cu_q[3:] = -1
+    op.out.fill_(3.0)
+    op.lse.fill_(3.0)
+    out = op.run()
+    torch.cuda.synchronize()
+    assert_device_band(out[:81].cpu(), op.lse[:81].cpu(), expected[:81], expected_lse[:81])
+    assert not out[81:].any() and not op.lse[81:].any()
+
+
+def test_selection_rules():
+    case, ori_scale, cmp_scale, _ = load_case("grouped_c4")
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    with pytest.raises(ValueError, match="Query grouping requires"):
+        PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2)
+    case, ori_scale, cmp_scale, _ = load_case("grouped_c128")
+    with pytest.raises(ValueError, match="query_group must be"):
+        PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=4)
