@@ -589,7 +589,7 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 constexpr int kLookahead = 1;
 constexpr int32_t kRowsInMap = 0x7ffffff0;      // rows the gather tensor maps span; row ids at or above read as zeros
 
-template <int RATIO, bool TMA, bool GROUP>
+template <int RATIO, bool TMA, bool GROUP, uint32_t STAGES = kStages>
 __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan,
                               uint32_t set, uint32_t pw, uint32_t lane, const CUtensorMap *ori_map, const CUtensorMap *cmp_map,
                               const CUtensorMap *cmp_page_map)
@@ -692,7 +692,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
         for (uint32_t u = 0; u < (uint32_t)kLookahead; ++u) {
             if (cc.done) goto drain;
             const uint32_t t = 2u * issued + set;          // position of the tile in the CTA's sequence
-            const uint32_t stage = t % kStages, pass = t / kStages;
+            const uint32_t stage = t % STAGES, pass = t / STAGES;
             if (!wait_phase<2>(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
             const bool ori = cc.j < (GROUP ? pair_original_tiles(cc.position, pair_tokens(cc.batch)) : ori_tiles);
             const int32_t id = row_ring[u * 32];
@@ -737,10 +737,13 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 }
                 cp_async_commit();
                 ++issued;
-                if (issued - signalled == 2) {            // keep one tile in flight behind the newest
-                    cp_async_wait<1>();
+                // keep one tile in flight behind the newest (with two stages a set owns one stage, so
+                // its next tile cannot start before this one has been handed over and consumed)
+                constexpr uint32_t kInFlight = STAGES >= 3 ? 2 : 1;
+                if (issued - signalled == kInFlight) {
+                    cp_async_wait<kInFlight - 1>();
                     fence_proxy_async_smem();
-                    mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % kStages));
+                    mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % STAGES));
                     ++signalled;
                 }
             }
@@ -752,7 +755,7 @@ drain:
     cp_async_wait<0>();
     fence_proxy_async_smem();
     while (signalled < issued) {
-        mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % kStages));
+        mbar_arrive(sm.bar(kBarFull + (2u * signalled + set) % STAGES));
         ++signalled;
     }
 }
@@ -1574,14 +1577,14 @@ cudaError_t launch_decode_paired(const SharedKVArgs &a, const CUtensorMap &ori_m
     const bool cached = device >= 0 && device < kMaxDevices;
     const uint64_t bit = cached ? 1ull << device : 0ull;
     if (!cached || !(configured.load(std::memory_order_relaxed) & bit)) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel_paired<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytesPaired);
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel_paired<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_relaxed);
     }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(grid);
     config.blockDim = dim3(kThreads);
-    config.dynamicSmemBytes = kSmemBytesPaired;
+    config.dynamicSmemBytes = kSmemBytes;
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

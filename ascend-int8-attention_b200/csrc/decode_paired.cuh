@@ -2,12 +2,13 @@
 //
 // Chunked prefill hands the kernel several query tokens per request.  Walked one by one, adjacent
 // tokens fetch almost the same keys: the same compressed prefix and windows that differ by one row.
-// Here two adjacent tokens of a request form ONE item.  Its tiles are fetched once; every tile is
-// then visited twice, once per token, and a visit is exactly what a tile is in decode_kernel: one
-// S = K.Q^T product, one softmax step with the token's own running state and validity, one
-// O = K^T.P product, one accumulate step.  The shapes of the products, the shared-memory tile, the
-// tensor-memory buffers and the barriers are those of decode_kernel; what changes is who owns which
-// state, and that a ring stage is released after its last visit.
+// Here two adjacent tokens of a request form ONE item, and both tokens ride through every product:
+//   S[128 keys, 32] = KV[128, 512] . Qcodes[32, 512]^T     Q rows 16 t + 8 plane + head
+//   O[512, 32]      = KV^T[512, 128] . P[128, 32]          P columns in the same order
+// (t = token of the pair, plane 0 = high codes, 1 = residual codes).  A tile is fetched once and
+// costs one pass through the tensor core, the softmax warps and the accumulate warps for the two
+// tokens together; each token keeps its own validity mask, running maximum, sum and accumulators.
+// decode_kernel's warp roles, barriers, work-item cursors and producers are reused as they are.
 //
 // Arithmetic: the reference's tiled oracle with query_group = 2 (npu_sparse_attn_sharedkv_int8/
 // reference.py:229-234,243-245): the original rows of an item are the union of its tokens' windows,
@@ -20,16 +21,30 @@
 // begins, so there are no partial states and no merges.  The reference's grouped plans are
 // unsplit too (attention.py:121-122: "Grouped-query kernel requires one KV partition").
 //
-// Query codes: a ring of three 8 KB buffers.  An item needs one set of codes per token and cache
-// kind it has tiles of ("uses", in the order original/token 0, original/token 1, compressed/token 0,
-// compressed/token 1); the n-th use of the CTA's life lives in buffer n mod 3.  The codes of a
-// use are no longer read after the last S product of its kind and token, which for the first
-// token is one visit before the kind's last: the buffer then takes the use three places on while
-// the item is still running.  Both query warps walk every use and wait for its buffer (the warp of
-// the use's kind encodes, the other only reports that it has been there), so that neither can
-// fall a whole barrier phase behind the other.
+// Shared memory: the 32-row query codes (16 KB a set) and the 32-column P codes do not fit beside
+// three 64 KB key tiles, so the key ring has two stages and the third stage's 64 KB hold them.  Two
+// stages are enough here: a tile now carries the work of two tokens, so fetching the next tile
+// takes longer than consuming this one less often than in decode_kernel.
+//
+// Query codes: a ring of three buffers.  An item needs one set of codes per cache kind it has tiles
+// of ("uses": original, then compressed); the n-th use of the CTA's life lives in buffer n mod 3,
+// so the next item's codes are written while this item's are read.  Both query warps walk every
+// use and wait for its buffer (the warp of the use's kind encodes, the other only reports that it
+// has been there), so that neither can fall a whole barrier phase behind the other.
 
-// ------------------------------------------------------------------ what an item says about its visits
+constexpr uint32_t kPairStages = 2;
+// shared memory inside what is decode_kernel's third key tile; everything else keeps its place
+constexpr uint32_t kSmQ2 = kPairStages * kTileBytes;          // 3 buffers x [32 rows x 512 B], 128-byte swizzle
+constexpr uint32_t kSmP2 = kSmQ2 + 3 * 16384;                 // 2 buffers x [2 tokens][128 keys][16 B]
+constexpr uint32_t kSmRed2 = kSmP2 + 2 * 4096;                // FP32 [2 halves][2 parities][2 tokens][4 warps][4]
+constexpr uint32_t kSmAlpha2 = kSmRed2 + 512;                 // FP32 [8 items][2 tokens][2 kinds][8]: alpha * softmax_scale
+constexpr uint32_t kSmFinal2 = kSmAlpha2 + 8 * 128;           // FP32 [8 items][2 tokens][16]: m[8], l[8]
+static_assert(kSmFinal2 + 8 * 128 <= kStages * kTileBytes, "the paired kernel's extras live inside the third key tile");
+// tensor memory: S[b] at 32 b (32 columns), O[b] at 64 + 128 b as four 32-column channel blocks
+constexpr uint32_t kTmemCols2 = 512;
+constexpr uint32_t kColS2 = 0, kColO2 = 64;
+
+// ------------------------------------------------------------------ what an item says about its tiles
 struct PairShape {
     uint32_t tokens;        // 1 or 2
     uint32_t windows;       // original tiles (the window union)
@@ -46,7 +61,7 @@ __device__ __forceinline__ PairShape pair_shape(uint32_t batch_word, int32_t fir
     return s;
 }
 __device__ __forceinline__ PairShape pair_shape(const Item &it) { return pair_shape(it.batch, it.position, it.tile_end); }
-// May query token at `position` see this key?  `row` is the logical row of the original cache
+// May the query token at `position` see this key?  `row` is the logical row of the original cache
 // (kind 0) or the compressed row (kind 1).
 __device__ __forceinline__ bool pair_sees(int32_t position, uint32_t kind, uint32_t row)
 {
@@ -55,16 +70,9 @@ __device__ __forceinline__ bool pair_sees(int32_t position, uint32_t kind, uint3
     return kind == 0 ? (row <= pos && row + kWindow > pos) : row < (pos + 1u) / 128u;
 }
 
-// shared memory of the paired kernel: decode_kernel's map, then the second token's scale factors
-// and final states
-constexpr uint32_t kSmAlpha1 = kSmPlan + 48;              // FP32 [8 items][2 kinds][8] for token 1
-constexpr uint32_t kSmFinal1 = kSmAlpha1 + 8 * 64;        // [8 items][16]: m[8], l[8] of token 1
-constexpr uint32_t kSmemBytesPaired = kSmFinal1 + 8 * 64 + 1024;
-static_assert(kSmemBytesPaired <= 232448, "dynamic shared memory limit of sm_100");
-
 // ------------------------------------------------------------------ work split of the paired kernel
 // Groups, not tokens, are the unit: request b has ceil(tokens_b / 2) groups.  The flat cost list
-// (kItemCost per group plus one unit per visit) is cut into `grid` ranges as in plan_cta, but a
+// (kItemCost per group plus one unit per tile) is cut into `grid` ranges as in plan_cta, but a
 // group is never cut: it goes to the CTA in whose range its first unit lies.  The group with index
 // g is workspace entry g, so a CTA's items are consecutive entries.
 struct PairPlanScratch {
@@ -73,6 +81,7 @@ struct PairPlanScratch {
     int32_t cu[kPlanStaged];          // cuQ of the live requests
     uint32_t groups[kPlanStaged];     // exclusive prefix of the groups per request
 };
+static_assert(sizeof(PairPlanScratch) <= kPairStages * kTileBytes, "the plan's scratch is the key ring");
 __device__ __forceinline__ uint32_t owner_of_group(const uint32_t *groups, uint32_t live_batch, uint32_t g)
 {
     uint32_t lo = 0, hi = live_batch - 1;
@@ -126,7 +135,7 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
     const uint32_t per = (total_groups + kThreads - 1) / kThreads;
     const uint32_t g_begin = min(tid * per, total_groups), g_end = min(g_begin + per, total_groups);
     struct Group {
-        uint32_t token, batch_word, tiles, visits;
+        uint32_t token, batch_word, tiles;
         int32_t position;
     };
     auto describe = [&](uint32_t g) {
@@ -139,11 +148,10 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
         d.position = split::token_position(seq[b], sc->cu[b + 1], t0);
         d.batch_word = b | (tokens == 2u ? kPairBit : 0u);
         d.tiles = pair_original_tiles(d.position, tokens) + (pair_compressed_rows(d.position, tokens) + kTileKeys - 1u) / kTileKeys;
-        d.visits = d.tiles * tokens;
         return d;
     };
     uint32_t my_cost = 0;
-    for (uint32_t g = g_begin; g < g_end; ++g) my_cost += split::kItemCost + describe(g).visits;
+    for (uint32_t g = g_begin; g < g_end; ++g) my_cost += split::kItemCost + describe(g).tiles;
     uint32_t total;
     uint32_t start = block_exclusive_scan(my_cost, sc->scan, total);
     const uint32_t quota = split::quota_of(total, grid);
@@ -162,7 +170,7 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
             ++found;
             tiles += d.tiles;
         }
-        start += split::kItemCost + d.visits;
+        start += split::kItemCost + d.tiles;
     }
     if (found) {
         atomicMin(&result->first, my_entry);
@@ -185,10 +193,11 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
 
 // ------------------------------------------------------------------ query warps (18: original kind, 19: compressed kind)
 // Lane l owns channels 16 l .. 16 l + 15.  Encodes the eight query rows of one token for one cache
-// kind into a code buffer (rows h and 8 + h, swizzled) and publishes alpha * softmax_scale per head;
-// the arithmetic is query_loop's (csrc/kernels/c8/vector.h:179-213 of the reference).
+// kind into rows `first_row` + head (high codes) and `first_row` + 8 + head (residual codes) of a
+// 32-row code buffer and publishes alpha * softmax_scale per head; the arithmetic is query_loop's
+// (csrc/kernels/c8/vector.h:179-213 of the reference).
 __device__ __forceinline__ void pair_encode_token(const SharedKVArgs &p, uint32_t token, const float (&sc)[16], char *qdst,
-                                                  float *alphas, uint32_t lane)
+                                                  uint32_t first_row, float *alphas, uint32_t lane)
 {
     const uint4 *src = reinterpret_cast<const uint4 *>(p.q + (uint64_t)token * 8192u) + lane * 2u;
     uint4 raw[4][2];                               // four heads of loads in flight at a time
@@ -228,14 +237,13 @@ __device__ __forceinline__ void pair_encode_token(const SharedKVArgs &p, uint32_
                 hi[w] = __byte_perm(__byte_perm(ch[0], ch[1], 0x0040), __byte_perm(ch[2], ch[3], 0x0040), 0x5410);
                 lo[w] = __byte_perm(__byte_perm(cl[0], cl[1], 0x0040), __byte_perm(cl[2], cl[3], 0x0040), 0x5410);
             }
-            *reinterpret_cast<uint4 *>(qdst + tile_offset(h, lane, 2048u)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4 *>(qdst + tile_offset(8u + h, lane, 2048u)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4 *>(qdst + tile_offset(first_row + h, lane, 4096u)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4 *>(qdst + tile_offset(first_row + 8u + h, lane, 4096u)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             if (lane == 0) alphas[h] = __fmul_rn(alpha, p.softmaxScale);
             raw[0][0] = raw[1][0]; raw[0][1] = raw[1][1]; raw[1][0] = raw[2][0]; raw[1][1] = raw[2][1];
             raw[2][0] = raw[3][0]; raw[2][1] = raw[3][1];
         }
     }
-    fence_proxy_async_smem();
 }
 
 __device__ void pair_query_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan, uint32_t kind,
@@ -266,16 +274,18 @@ __device__ void pair_query_loop(const SharedKVArgs &p, const Shared &sm, const I
             }
         }
         for (uint32_t use_kind = 0; use_kind < shape.kinds; ++use_kind) {
-            for (uint32_t token = 0; token < shape.tokens; ++token) {
-                // the use that had the buffer before must no longer be read
-                if (round > 0 && !wait_phase<3>(sm, kBarQFree + buf, (round - 1u) & 1u)) return;
-                if (use_kind == kind) {
-                    float *alphas = reinterpret_cast<float *>(sm.ptr + (token ? kSmAlpha1 : kSmAlpha)) + (k & 7u) * 16u + kind * 8u;
-                    pair_encode_token(p, it.token + token, sc, sm.ptr + kSmQ + buf * 8192u, alphas, lane);
+            // the use that had the buffer before must no longer be read
+            if (round > 0 && !wait_phase<3>(sm, kBarQFree + buf, (round - 1u) & 1u)) return;
+            if (use_kind == kind) {
+                // rows of a token the item does not have keep whatever they held: their S columns are never read
+                for (uint32_t token = 0; token < shape.tokens; ++token) {
+                    float *alphas = reinterpret_cast<float *>(sm.ptr + kSmAlpha2) + ((k & 7u) * 2u + token) * 16u + kind * 8u;
+                    pair_encode_token(p, it.token + token, sc, sm.ptr + kSmQ2 + buf * 16384u, 16u * token, alphas, lane);
                 }
-                mbar_arrive(sm.bar(kBarQReady + buf));
-                if (++buf == 3u) { buf = 0; ++round; }
+                fence_proxy_async_smem();
             }
+            mbar_arrive(sm.bar(kBarQReady + buf));
+            if (++buf == 3u) { buf = 0; ++round; }
         }
         cursor_next_item(cur, items, plan);
     }
@@ -284,173 +294,104 @@ __device__ void pair_query_loop(const SharedKVArgs &p, const Shared &sm, const I
 // ------------------------------------------------------------------ S = K.Q^T issuer (warp 16)
 __device__ void pair_qk_loop(const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
 {
-    constexpr uint32_t kIdescQK = idesc_i8(128, 16, 0, 0);
+    constexpr uint32_t kIdescQK = idesc_i8(128, 32, 0, 0);
     const bool leader = elect_one();
     const uint32_t count = __shfl_sync(0xffffffffu, plan.count, 0);
     Cursor cq;
     cursor_init(cq, items, plan);
-    uint32_t t = 0, v = 0, uses = 0;       // tiles fetched / visits issued / code uses before this item
+    uint32_t t = 0, uses = 0;              // tiles issued / code uses before this item
     for (uint32_t k = 0; k < count; ++k) {
         const PairShape shape = pair_shape(__shfl_sync(0xffffffffu, cq.it.batch, 0), (int32_t)__shfl_sync(0xffffffffu, (uint32_t)cq.it.position, 0),
                                            __shfl_sync(0xffffffffu, cq.it.tile_end, 0));
         for (uint32_t j = 0; j < shape.tiles; ++j, ++t) {
-            const uint32_t stage = t % kStages, kind = j < shape.windows ? 0u : 1u;
+            const uint32_t buf = t & 1u, ph = (t >> 1) & 1u;          // key stage and S buffer alternate together
+            const uint32_t kind = j < shape.windows ? 0u : 1u, use = uses + kind;
+            const uint32_t b = use % 3u;
             const bool first_of_kind = j == 0 || j == shape.windows;
             const bool last_of_kind = j + 1u == shape.windows || j + 1u == shape.tiles;
-            if (!wait_phase<3>(sm, kBarFull + stage, (t / kStages) & 1u)) return;
-            for (uint32_t token = 0; token < shape.tokens; ++token, ++v) {
-                const uint32_t use = uses + kind * shape.tokens + token;
-                const uint32_t b = use % 3u, buf = v & 1u, ph = (v >> 1) & 1u;
-                if (first_of_kind && !wait_phase<3>(sm, kBarQReady + b, (use / 3u) & 1u)) return;
-                if (!wait_phase<3>(sm, kBarSFree + buf, ph ^ 1u)) return;
-                tc_fence_after();
-                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-                const uint32_t qb = sm.base + kSmQ + b * 8192u;
-                const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
+            if (first_of_kind && !wait_phase<3>(sm, kBarQReady + b, (use / 3u) & 1u)) return;
+            if (!wait_phase<3>(sm, kBarFull + buf, ph)) return;
+            if (!wait_phase<3>(sm, kBarSFree + buf, ph ^ 1u)) return;
+            tc_fence_after();
+            const uint32_t kv = sm.base + kSmKv + buf * kTileBytes;
+            const uint32_t qb = sm.base + kSmQ2 + b * 16384u;
+            const uint64_t a0 = smem_desc(kv, 16u, 1024u, kSwizzle128), b0 = smem_desc(qb, 16u, 1024u, kSwizzle128);
 #pragma unroll 1
-                for (uint32_t seg = 0; seg < 4; ++seg) {
+            for (uint32_t seg = 0; seg < 4; ++seg) {
 #pragma unroll
-                    for (uint32_t part = 0; part < 4; ++part)
-                        if (leader)
-                            mma_i8(tmem + kColS + buf * 16u, a0 + ((seg * kSegBytes + part * 32u) >> 4),
-                                   b0 + ((seg * 2048u + part * 32u) >> 4), kIdescQK, seg | part);
-                }
-                if (leader) {
-                    mma_commit(sm.bar(kBarSFull + buf));
-                    if (last_of_kind) mma_commit(sm.bar(kBarQFree + b));
-                }
+                for (uint32_t part = 0; part < 4; ++part)
+                    if (leader)
+                        mma_i8(tmem + kColS2 + buf * 32u, a0 + ((seg * kSegBytes + part * 32u) >> 4), b0 + ((seg * 4096u + part * 32u) >> 4),
+                               kIdescQK, seg | part);
+            }
+            if (leader) {
+                mma_commit(sm.bar(kBarSFull + buf));
+                if (last_of_kind) mma_commit(sm.bar(kBarQFree + b));
             }
         }
-        uses += shape.tokens * shape.kinds;
+        uses += shape.kinds;
         cursor_next_item(cq, items, plan);
     }
 }
 
 // ------------------------------------------------------------------ O = K^T.P issuer (warp 17)
-__device__ void pair_pv_loop(const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
+__device__ void pair_pv_loop(const Shared &sm, const PlanResult &plan, uint32_t tmem)
 {
-    constexpr uint32_t kIdescPV = idesc_i8(128, 16, 1, 1);
+    constexpr uint32_t kIdescPV = idesc_i8(128, 32, 1, 1);
     const bool leader = elect_one();
-    const uint32_t count = __shfl_sync(0xffffffffu, plan.count, 0);
-    Cursor cp;
-    cursor_init(cp, items, plan);
-    uint32_t t = 0, v = 0;
-    for (uint32_t k = 0; k < count; ++k) {
-        const uint32_t tokens = pair_tokens(__shfl_sync(0xffffffffu, cp.it.batch, 0));
-        const uint32_t tiles = __shfl_sync(0xffffffffu, cp.it.tile_end, 0);
-        for (uint32_t j = 0; j < tiles; ++j, ++t) {
-            const uint32_t stage = t % kStages;
-            for (uint32_t token = 0; token < tokens; ++token, ++v) {
-                const uint32_t buf = v & 1u, ph = (v >> 1) & 1u;
-                if (!wait_phase<3>(sm, kBarPReady + buf, ph)) return;
-                if (!wait_phase<3>(sm, kBarOFree + buf, ph ^ 1u)) return;
-                tc_fence_after();
-                const uint32_t kv = sm.base + kSmKv + stage * kTileBytes;
-                const uint32_t pb = sm.base + kSmP + buf * 2048u;
-                const uint64_t a0 = smem_desc(kv, kSegBytes, 1024u, kSwizzle128), b0 = smem_desc(pb, 128u, 2048u, kSwizzleNone);
+    const uint32_t tiles = __shfl_sync(0xffffffffu, plan.tiles, 0);
+    for (uint32_t t = 0; t < tiles; ++t) {
+        const uint32_t buf = t & 1u, ph = (t >> 1) & 1u;
+        if (!wait_phase<3>(sm, kBarPReady + buf, ph)) return;
+        if (!wait_phase<3>(sm, kBarOFree + buf, ph ^ 1u)) return;
+        tc_fence_after();
+        const uint32_t kv = sm.base + kSmKv + buf * kTileBytes;
+        const uint32_t pb = sm.base + kSmP2 + buf * 4096u;
+        // P: 8-key x 16-byte core matrices, 128 bytes apart along the keys, the two tokens' 16 columns 2048 bytes apart
+        const uint64_t a0 = smem_desc(kv, kSegBytes, 1024u, kSwizzle128), b0 = smem_desc(pb, 128u, 2048u, kSwizzleNone);
 #pragma unroll 1
-                for (uint32_t mb = 0; mb < 4; ++mb) {
+        for (uint32_t mb = 0; mb < 4; ++mb) {
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4; ++kk)
-                        if (leader)
-                            mma_i8(tmem + kColO + buf * 64u + mb * 16u, a0 + ((mb * kSegBytes + kk * 4096u) >> 4),
-                                   b0 + ((kk * 512u) >> 4), kIdescPV, kk);
-                }
-                if (leader) {
-                    mma_commit(sm.bar(kBarOFull + buf));
-                    if (token + 1u == tokens) mma_commit(sm.bar(kBarEmpty + stage));      // the stage's last reader
-                }
-            }
+            for (uint32_t kk = 0; kk < 4; ++kk)
+                if (leader)
+                    mma_i8(tmem + kColO2 + buf * 128u + mb * 32u, a0 + ((mb * kSegBytes + kk * 4096u) >> 4), b0 + ((kk * 512u) >> 4),
+                           kIdescPV, kk);
         }
-        cursor_next_item(cp, items, plan);
+        if (leader) {
+            mma_commit(sm.bar(kBarOFull + buf));
+            mma_commit(sm.bar(kBarEmpty + buf));      // the stage's last reader
+        }
     }
 }
 
 // ------------------------------------------------------------------ softmax warps (0-7)
-// One visit: the softmax step of softmax_loop for one token of the item, with the token's own
-// running maximum and sum.  `valid` already holds the token's own mask.
-struct PairVisit {
-    uint32_t v;             // visit number of the CTA
-    uint32_t kind;
-    const float *alphas;    // alpha * softmax_scale of this token, [2 kinds][8]
+// Thread (half, key) owns heads 4 half .. 4 half + 3 of key `key` for both tokens of the item.
+struct PairState {
+    float m[4], l[4];
 };
-__device__ __forceinline__ bool pair_softmax_visit(const Shared &sm, const PairVisit &visit, bool valid, float (&m)[4], float (&l)[4],
-                                                   uint32_t half, uint32_t key, uint32_t tmem_lane, float *red,
-                                                   uint32_t &group_phase)
+// One token's share of a tile's softmax step after the maxima are known: running state, rescale
+// factors, P codes (packed: .x high plane, .y residual plane).
+__device__ __forceinline__ uint2 pair_softmax_token(PairState &st, const float (&logit)[4], const float4 &q0, const float4 &q1, const float4 &q2,
+                                                    const float4 &q3, float (&r)[4])
 {
-    const uint32_t lane = key & 31u, warp = key >> 5;
-    const uint32_t buf = visit.v & 1u, ph = (visit.v >> 1) & 1u;
-    if (!wait_phase<0>(sm, kBarSFull + buf, ph)) return false;
-    tc_fence_after();
-    uint32_t s_hi[4], s_lo[4];
-    tmem_ld4(tmem_lane + kColS + buf * 16u + half * 4u, s_hi);
-    tmem_ld4(tmem_lane + kColS + buf * 16u + 8u + half * 4u, s_lo);
-    tmem_wait_ld();
-    tc_fence_before();
-    mbar_arrive(sm.bar(kBarSFree + buf));
-
-    float logit[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float dots = __fadd_rn((float)(int)s_hi[i], __fmul_rn((float)(int)s_lo[i], kInv127));
-        logit[i] = valid ? __fmul_rn(dots, visit.alphas[visit.kind * 8u + half * 4u + i]) : kMasked;
-    }
-    const float wmax = warp_reduce4<true>(logit, lane);
-    float *slot_red = red + (visit.v & 1u) * 16u;
-    if ((lane & 7u) == 0) slot_red[warp * 4u + (lane >> 3)] = wmax;
-    if (!group_sync<0>(sm, half, group_phase)) return false;
-    float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (visit.v & 7u) * 16u;
-    int p_hi[4], p_lo[4];
-    float r[4];
-    const float4 q0 = reinterpret_cast<const float4 *>(slot_red)[0], q1 = reinterpret_cast<const float4 *>(slot_red)[1];
-    const float4 q2 = reinterpret_cast<const float4 *>(slot_red)[2], q3 = reinterpret_cast<const float4 *>(slot_red)[3];
     const float tmaxes[4] = {fmaxf(fmaxf(q0.x, q1.x), fmaxf(q2.x, q3.x)), fmaxf(fmaxf(q0.y, q1.y), fmaxf(q2.y, q3.y)),
                              fmaxf(fmaxf(q0.z, q1.z), fmaxf(q2.z, q3.z)), fmaxf(fmaxf(q0.w, q1.w), fmaxf(q2.w, q3.w))};
+    int p_hi[4], p_lo[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float mnew = fmaxf(m[i], tmaxes[i]);
-        r[i] = mnew == m[i] ? 1.f : fast_exp(__fsub_rn(m[i], mnew));
+        const float mnew = fmaxf(st.m[i], tmaxes[i]);
+        r[i] = mnew == st.m[i] ? 1.f : fast_exp(__fsub_rn(st.m[i], mnew));
         const float w = fast_exp(__fsub_rn(logit[i], mnew));
-        l[i] = __fmaf_rn(l[i], r[i], w);
+        st.l[i] = __fmaf_rn(st.l[i], r[i], w);
         const float w127 = __fmul_rn(w, 127.f);
         const float shifted = __fadd_rn(w127, 12582912.f);
         const float hf = __fsub_rn(shifted, 12582912.f);
         p_hi[i] = (int)(__float_as_uint(shifted) - 0x4b400000u);
         const float shifted_lo = __fadd_rn(__fmul_rn(__fsub_rn(w127, hf), 127.f), 12582912.f);
         p_lo[i] = (int)(__float_as_uint(shifted_lo) - 0x4b400000u);
-        m[i] = mnew;
+        st.m[i] = mnew;
     }
-    if (key == 0) {
-        *reinterpret_cast<float4 *>(ring + half * 4u) = make_float4(r[0], r[1], r[2], r[3]);
-        mbar_arrive(sm.bar(kBarRescale + (visit.v & 7u)));
-    }
-    // the O product that read this P buffer two visits ago must be complete before it is rewritten
-    if (visit.v >= 2u && !wait_phase<0>(sm, kBarOFull + buf, ph ^ 1u)) return false;
-    uint32_t *pdst = reinterpret_cast<uint32_t *>(sm.ptr + kSmP + buf * 2048u + key * 16u);
-    pdst[half] = pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]);
-    pdst[2u + half] = pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]);
-    fence_proxy_async_smem();
-    mbar_arrive(sm.bar(kBarPReady + buf));
-    return true;
-}
-
-// Sum of the per-thread partial sums of one token, handed with its maxima to the accumulate warps.
-__device__ __forceinline__ bool pair_softmax_final(const Shared &sm, const float (&m)[4], const float (&l)[4], float *fin, uint32_t half,
-                                                   uint32_t key, float *red, uint32_t &group_phase)
-{
-    const uint32_t lane = key & 31u, warp = key >> 5;
-    const float wsum = warp_reduce4<false>(l, lane);
-    if (!group_sync<0>(sm, half, group_phase)) return false;       // everyone is past the last reads of `red`
-    if ((lane & 7u) == 0) red[warp * 4u + (lane >> 3)] = wsum;
-    if (!group_sync<0>(sm, half, group_phase)) return false;
-    if (key == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            fin[half * 4u + i] = m[i];
-            fin[8u + half * 4u + i] = __fadd_rn(__fadd_rn(red[i], red[4 + i]), __fadd_rn(red[8 + i], red[12 + i]));
-        }
-    }
-    return true;
+    return make_uint2(pack4(p_hi[0], p_hi[1], p_hi[2], p_hi[3]), pack4(p_lo[0], p_lo[1], p_lo[2], p_lo[3]));
 }
 
 __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
@@ -458,7 +399,7 @@ __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const
     const uint32_t half = threadIdx.x >> 7, key = threadIdx.x & 127u;
     const uint32_t lane = key & 31u, warp = key >> 5;
     const uint32_t tmem_lane = tmem + ((warp * 32u) << 16);
-    float *red = reinterpret_cast<float *>(sm.ptr + kSmRed) + half * 32u;
+    float *red = reinterpret_cast<float *>(sm.ptr + kSmRed2) + half * 64u;       // [2 parities][2 tokens][4 warps][4], per half
     uint32_t group_phase = 0;
     float sink[4];
 #pragma unroll
@@ -466,89 +407,102 @@ __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const
 
     Cursor cur;
     cursor_init(cur, items, plan);
-    uint32_t t = 0, v = 0;
+    uint32_t t = 0;                                // tiles consumed so far by this CTA
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
         const PairShape shape = pair_shape(it);
         const uint32_t start = pair_window_start(it.position);
-        float m0[4], l0[4], m1[4], l1[4];
+        const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha2) + (k & 7u) * 32u;      // [2 tokens][2 kinds][8]
+        PairState s0, s1;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            m0[i] = m1[i] = sink[i];
-            l0[i] = l1[i] = key == 0 ? 1.f : 0.f;
+            s0.m[i] = s1.m[i] = sink[i];
+            s0.l[i] = s1.l[i] = key == 0 ? 1.f : 0.f;
         }
-        PairVisit visit;
         for (uint32_t j = 0; j < shape.tiles; ++j, ++t) {
-            const uint32_t stage = t % kStages;
-            if (!wait_phase<0>(sm, kBarFull + stage, (t / kStages) & 1u)) return;
-            const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[stage * 4u + warp];
+            const uint32_t buf = t & 1u, ph = (t >> 1) & 1u;
+            const uint32_t kind = j < shape.windows ? 0u : 1u;
+            if (!wait_phase<0>(sm, kBarFull + buf, ph)) return;
+            const uint32_t mask_word = reinterpret_cast<volatile uint32_t *>(sm.ptr + kSmMask)[buf * 4u + warp];
             const bool has_key = (mask_word >> lane) & 1u;
-            visit.kind = j < shape.windows ? 0u : 1u;
             // what this key is to each token: a window row (logical row number) or a compressed row
-            const uint32_t row = visit.kind == 0 ? start + j * kTileKeys + key : (j - shape.windows) * kTileKeys + key;
-            {
-                visit.v = v++;
-                visit.alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha) + (k & 7u) * 16u;
-                if (!pair_softmax_visit(sm, visit, has_key && pair_sees(it.position, visit.kind, row), m0, l0, half, key, tmem_lane, red,
-                                        group_phase))
-                    return;
+            const uint32_t row = kind == 0 ? start + j * kTileKeys + key : (j - shape.windows) * kTileKeys + key;
+            const bool valid0 = has_key && pair_sees(it.position, kind, row);
+            const bool valid1 = has_key && shape.tokens == 2u && pair_sees(it.position + 1, kind, row);
+            if (!wait_phase<0>(sm, kBarSFull + buf, ph)) return;
+            tc_fence_after();
+            uint32_t a_hi[4], a_lo[4], b_hi[4], b_lo[4];
+            tmem_ld4(tmem_lane + kColS2 + buf * 32u + half * 4u, a_hi);
+            tmem_ld4(tmem_lane + kColS2 + buf * 32u + 8u + half * 4u, a_lo);
+            tmem_ld4(tmem_lane + kColS2 + buf * 32u + 16u + half * 4u, b_hi);
+            tmem_ld4(tmem_lane + kColS2 + buf * 32u + 24u + half * 4u, b_lo);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(sm.bar(kBarSFree + buf));
+
+            float logit0[4], logit1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float d0 = __fadd_rn((float)(int)a_hi[i], __fmul_rn((float)(int)a_lo[i], kInv127));
+                const float d1 = __fadd_rn((float)(int)b_hi[i], __fmul_rn((float)(int)b_lo[i], kInv127));
+                logit0[i] = valid0 ? __fmul_rn(d0, alphas[kind * 8u + half * 4u + i]) : kMasked;
+                logit1[i] = valid1 ? __fmul_rn(d1, alphas[16u + kind * 8u + half * 4u + i]) : kMasked;
             }
-            if (shape.tokens == 2u) {
-                visit.v = v++;
-                visit.alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha1) + (k & 7u) * 16u;
-                if (!pair_softmax_visit(sm, visit, has_key && pair_sees(it.position + 1, visit.kind, row), m1, l1, half, key, tmem_lane, red,
-                                        group_phase))
-                    return;
+            const float wmax0 = warp_reduce4<true>(logit0, lane), wmax1 = warp_reduce4<true>(logit1, lane);
+            float *slot_red = red + (t & 1u) * 32u;
+            if ((lane & 7u) == 0) {
+                slot_red[warp * 4u + (lane >> 3)] = wmax0;
+                slot_red[16u + warp * 4u + (lane >> 3)] = wmax1;
+            }
+            if (!group_sync<0>(sm, half, group_phase)) return;
+            const float4 *rows = reinterpret_cast<const float4 *>(slot_red);
+            float r0[4], r1[4];
+            const uint2 c0 = pair_softmax_token(s0, logit0, rows[0], rows[1], rows[2], rows[3], r0);
+            const uint2 c1 = pair_softmax_token(s1, logit1, rows[4], rows[5], rows[6], rows[7], r1);
+            if (key == 0) {
+                // rescale factors of this tile: r[8] of token 0, r[8] of token 1
+                float *ring = reinterpret_cast<float *>(sm.ptr + kSmRescale) + (t & 7u) * 16u;
+                *reinterpret_cast<float4 *>(ring + half * 4u) = make_float4(r0[0], r0[1], r0[2], r0[3]);
+                *reinterpret_cast<float4 *>(ring + 8u + half * 4u) = make_float4(r1[0], r1[1], r1[2], r1[3]);
+                mbar_arrive(sm.bar(kBarRescale + (t & 7u)));
+            }
+            // the O product that read this P buffer two tiles ago must be complete before it is rewritten
+            if (t >= 2u && !wait_phase<0>(sm, kBarOFull + buf, ph ^ 1u)) return;
+            uint32_t *pdst = reinterpret_cast<uint32_t *>(sm.ptr + kSmP2 + buf * 4096u + key * 16u);
+            pdst[half] = c0.x;
+            pdst[2u + half] = c0.y;
+            pdst[512u + half] = c1.x;              // token 1: 2048 bytes on
+            pdst[512u + 2u + half] = c1.y;
+            fence_proxy_async_smem();
+            mbar_arrive(sm.bar(kBarPReady + buf));
+        }
+
+        // denominators: sum the per-thread partial sums, hand (m, l) of both tokens to the accumulate warps
+        {
+            const float wsum0 = warp_reduce4<false>(s0.l, lane), wsum1 = warp_reduce4<false>(s1.l, lane);
+            if (!group_sync<0>(sm, half, group_phase)) return;   // everyone is past the last tile's reads of `red`
+            if ((lane & 7u) == 0) {
+                red[warp * 4u + (lane >> 3)] = wsum0;
+                red[16u + warp * 4u + (lane >> 3)] = wsum1;
+            }
+            if (!group_sync<0>(sm, half, group_phase)) return;
+            if (key == 0) {
+                float *fin = reinterpret_cast<float *>(sm.ptr + kSmFinal2) + (k & 7u) * 32u;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    fin[half * 4u + i] = s0.m[i];
+                    fin[8u + half * 4u + i] = __fadd_rn(__fadd_rn(red[i], red[4 + i]), __fadd_rn(red[8 + i], red[12 + i]));
+                    fin[16u + half * 4u + i] = s1.m[i];
+                    fin[24u + half * 4u + i] = __fadd_rn(__fadd_rn(red[16 + i], red[20 + i]), __fadd_rn(red[24 + i], red[28 + i]));
+                }
+                mbar_arrive(sm.bar(kBarItemDone + (k & 7u)));
             }
         }
-        if (!pair_softmax_final(sm, m0, l0, reinterpret_cast<float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u, half, key, red, group_phase))
-            return;
-        if (shape.tokens == 2u &&
-            !pair_softmax_final(sm, m1, l1, reinterpret_cast<float *>(sm.ptr + kSmFinal1) + (k & 7u) * 16u, half, key, red, group_phase))
-            return;
-        if (key == 0) mbar_arrive(sm.bar(kBarItemDone + (k & 7u)));
         cursor_next_item(cur, items, plan);
     }
 }
 
 // ------------------------------------------------------------------ accumulate warps (8-11)
-__device__ __forceinline__ bool pair_accumulate_visit(const Shared &sm, uint32_t v, float s_mb0, float s_mb1, float s_mb2, float s_mb3,
-                                                      float (&acc)[4][8], uint32_t tmem_lane)
-{
-    const uint32_t buf = v & 1u, ph = (v >> 1) & 1u, slot = v & 7u;
-    if (!wait_phase<1>(sm, kBarRescale + slot, (v >> 3) & 1u)) return false;
-    const float4 *ring = reinterpret_cast<const float4 *>(sm.ptr + kSmRescale + slot * 64u);
-    const float4 ra = ring[0], rb = ring[1];
-    const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
-    const bool rescale = (ra.x != 1.f) | (ra.y != 1.f) | (ra.z != 1.f) | (ra.w != 1.f) | (rb.x != 1.f) | (rb.y != 1.f) |
-                         (rb.z != 1.f) | (rb.w != 1.f);
-    if (rescale) {
-#pragma unroll
-        for (int mb = 0; mb < 4; ++mb)
-#pragma unroll
-            for (int h = 0; h < 8; ++h) acc[mb][h] = __fmul_rn(acc[mb][h], r[h]);
-    }
-    if (!wait_phase<1>(sm, kBarOFull + buf, ph)) return false;
-    tc_fence_after();
-    const float s[4] = {s_mb0, s_mb1, s_mb2, s_mb3};
-#pragma unroll
-    for (uint32_t mb = 0; mb < 4; ++mb) {
-        uint32_t o[16];
-        tmem_ld16(tmem_lane + kColO + buf * 64u + mb * 16u, o);
-        tmem_wait_ld();
-        if (mb == 3) {
-            tc_fence_before();
-            mbar_arrive(sm.bar(kBarOFree + buf));
-        }
-#pragma unroll
-        for (int h = 0; h < 8; ++h) {
-            const float dots = __fmaf_rn(small_int_to_float(o[8 + h]), kInv127, small_int_to_float(o[h]));
-            acc[mb][h] = __fmaf_rn(dots, s[mb], acc[mb][h]);
-        }
-    }
-    return true;
-}
-
 __device__ __forceinline__ void pair_store_token(const SharedKVArgs &p, uint32_t token, const float (&acc)[4][8], const float *fin, uint32_t ch)
 {
     __nv_bfloat16 *out = reinterpret_cast<__nv_bfloat16 *>(p.out) + (uint64_t)token * 4096u;
@@ -559,6 +513,20 @@ __device__ __forceinline__ void pair_store_token(const SharedKVArgs &p, uint32_t
         for (int mb = 0; mb < 4; ++mb) out[h * 512 + mb * 128 + ch] = __float2bfloat16_rn(__fmul_rn(acc[mb][h], inv));
     }
     if (p.lse && ch < 8) reinterpret_cast<float *>(p.lse)[(uint64_t)token * 8u + ch] = __fadd_rn(fin[ch], logf(fin[8 + ch]));
+}
+
+__device__ __forceinline__ void pair_rescale(float (&acc)[4][8], const float4 &ra, const float4 &rb)
+{
+    // once the running maxima have settled every factor is exactly 1 and the multiply is skipped
+    const bool rescale = (ra.x != 1.f) | (ra.y != 1.f) | (ra.z != 1.f) | (ra.w != 1.f) | (rb.x != 1.f) | (rb.y != 1.f) |
+                         (rb.z != 1.f) | (rb.w != 1.f);
+    if (rescale) {
+        const float r[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+        for (int mb = 0; mb < 4; ++mb)
+#pragma unroll
+            for (int h = 0; h < 8; ++h) acc[mb][h] = __fmul_rn(acc[mb][h], r[h]);
+    }
 }
 
 __device__ void pair_accumulate_loop(const SharedKVArgs &p, const Shared &sm, const Item *items, const PlanResult &plan, uint32_t tmem)
@@ -580,7 +548,7 @@ __device__ void pair_accumulate_loop(const SharedKVArgs &p, const Shared &sm, co
     }
     Cursor cur;
     cursor_init(cur, items, plan);
-    uint32_t v = 0;
+    uint32_t t = 0;
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
         const PairShape shape = pair_shape(it);
@@ -589,17 +557,41 @@ __device__ void pair_accumulate_loop(const SharedKVArgs &p, const Shared &sm, co
         for (int mb = 0; mb < 4; ++mb)
 #pragma unroll
             for (int h = 0; h < 8; ++h) acc0[mb][h] = acc1[mb][h] = 0.f;
-        for (uint32_t j = 0; j < shape.tiles; ++j) {
+        for (uint32_t j = 0; j < shape.tiles; ++j, ++t) {
+            const uint32_t buf = t & 1u, ph = (t >> 1) & 1u, slot = t & 7u;
+            if (!wait_phase<1>(sm, kBarRescale + slot, (t >> 3) & 1u)) return;
+            {
+                const float4 *ring = reinterpret_cast<const float4 *>(sm.ptr + kSmRescale + slot * 64u);
+                pair_rescale(acc0, ring[0], ring[1]);
+                pair_rescale(acc1, ring[2], ring[3]);
+            }
+            if (!wait_phase<1>(sm, kBarOFull + buf, ph)) return;
+            tc_fence_after();
             const uint32_t kind = j < shape.windows ? 0u : 1u;
-            if (!pair_accumulate_visit(sm, v++, sc[kind][0], sc[kind][1], sc[kind][2], sc[kind][3], acc0, tmem_lane)) return;
-            if (shape.tokens == 2u &&
-                !pair_accumulate_visit(sm, v++, sc[kind][0], sc[kind][1], sc[kind][2], sc[kind][3], acc1, tmem_lane))
-                return;
+#pragma unroll
+            for (uint32_t mb = 0; mb < 4; ++mb) {
+                uint32_t o0[16], o1[16];
+                tmem_ld16(tmem_lane + kColO2 + buf * 128u + mb * 32u, o0);
+                tmem_ld16(tmem_lane + kColO2 + buf * 128u + mb * 32u + 16u, o1);
+                tmem_wait_ld();
+                if (mb == 3) {
+                    tc_fence_before();
+                    mbar_arrive(sm.bar(kBarOFree + buf));
+                }
+                const float s = kind ? sc[1][mb] : sc[0][mb];
+#pragma unroll
+                for (int h = 0; h < 8; ++h) {
+                    const float d0 = __fmaf_rn(small_int_to_float(o0[8 + h]), kInv127, small_int_to_float(o0[h]));
+                    const float d1 = __fmaf_rn(small_int_to_float(o1[8 + h]), kInv127, small_int_to_float(o1[h]));
+                    acc0[mb][h] = __fmaf_rn(d0, s, acc0[mb][h]);
+                    acc1[mb][h] = __fmaf_rn(d1, s, acc1[mb][h]);
+                }
+            }
         }
         if (!wait_phase<1>(sm, kBarItemDone + (k & 7u), (k >> 3) & 1u)) return;
-        pair_store_token(p, it.token, acc0, reinterpret_cast<const float *>(sm.ptr + kSmFinal) + (k & 7u) * 16u, ch);
-        if (shape.tokens == 2u)
-            pair_store_token(p, it.token + 1u, acc1, reinterpret_cast<const float *>(sm.ptr + kSmFinal1) + (k & 7u) * 16u, ch);
+        const float *fin = reinterpret_cast<const float *>(sm.ptr + kSmFinal2) + (k & 7u) * 32u;
+        pair_store_token(p, it.token, acc0, fin, ch);
+        if (shape.tokens == 2u) pair_store_token(p, it.token + 1u, acc1, fin + 16, ch);
         cursor_next_item(cur, items, plan);
     }
 }
@@ -621,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const Shared
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     volatile uint32_t *misc = sm.misc();
     if (tid == 0) {
-        for (uint32_t s = 0; s < kStages; ++s) { mbar_init(sm.bar(kBarFull + s), TMA ? 4 : 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
+        for (uint32_t s = 0; s < kPairStages; ++s) { mbar_init(sm.bar(kBarFull + s), TMA ? 4 : 128); mbar_init(sm.bar(kBarEmpty + s), 1); }
         for (uint32_t b = 0; b < 2; ++b) {
             mbar_init(sm.bar(kBarSFull + b), 1); mbar_init(sm.bar(kBarSFree + b), 256);
             mbar_init(sm.bar(kBarPReady + b), 256); mbar_init(sm.bar(kBarOFull + b), 1); mbar_init(sm.bar(kBarOFree + b), 128);
@@ -636,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const Shared
         fence_mbar_init();
     }
     if (warp == kWarpMma) {
-        tmem_alloc(sm.base + kSmMisc, kTmemCols);
+        tmem_alloc(sm.base + kSmMisc, kTmemCols2);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -663,14 +655,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const Shared
             tma_prefetch_descriptor(&cmp_page_map);
         }
         const uint32_t set = warp >= kWarpProducerB ? 1u : 0u;
-        producer_loop<128, TMA, true>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map, &cmp_page_map);
+        producer_loop<128, TMA, true, kPairStages>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
+                                                   &cmp_page_map);
         cp_async_wait<0>();
     } else {
         if (warp >= kWarpQuery) {
             pair_query_loop(p, sm, items, plan, warp - kWarpQuery, lane);
         } else {
             if (warp == kWarpMma) pair_qk_loop(sm, items, plan, tmem);
-            else pair_pv_loop(sm, items, plan, tmem);
+            else pair_pv_loop(sm, plan, tmem);
             __syncwarp();
         }
     }
@@ -683,6 +676,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const Shared
     }
     if (warp == kWarpMma) {
         tc_fence_after();
-        tmem_dealloc(tmem, kTmemCols);
+        tmem_dealloc(tmem, kTmemCols2);
     }
 }
