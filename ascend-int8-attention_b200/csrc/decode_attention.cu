@@ -506,27 +506,10 @@ __device__ __noinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s
 constexpr uint32_t kPairBit = 0x80000000u;
 __device__ __forceinline__ uint32_t pair_tokens(uint32_t batch_word) { return (batch_word >> 31) + 1u; }
 __device__ __forceinline__ uint32_t pair_batch(uint32_t batch_word) { return batch_word & ~kPairBit; }
-// Position of the item's last token (negative: no token of the item sees a key).
-__device__ __forceinline__ int32_t pair_last_position(int32_t first_position, uint32_t tokens) { return first_position + (int32_t)tokens - 1; }
-__device__ __forceinline__ uint32_t pair_window_start(int32_t first_position)
-{
-    return first_position >= (int32_t)kWindow ? (uint32_t)first_position + 1u - kWindow : 0u;
-}
-// 128-key tiles of the window union of an item (1 or 2; 1 also when it has no row at all, so that
-// its output rows are written).
-__device__ __forceinline__ uint32_t pair_original_tiles(int32_t first_position, uint32_t tokens)
-{
-    const int32_t last = pair_last_position(first_position, tokens);
-    if (last < 0) return 1u;
-    const uint32_t rows = (uint32_t)last + 1u - pair_window_start(first_position);
-    return (rows + kTileKeys - 1u) / kTileKeys;
-}
-// Compressed rows an item walks: the prefix of its last token.
-__device__ __forceinline__ uint32_t pair_compressed_rows(int32_t first_position, uint32_t tokens)
-{
-    const int32_t last = pair_last_position(first_position, tokens);
-    return last < 0 ? 0u : ((uint32_t)last + 1u) / 128u;
-}
+using split::pair_compressed_rows;
+using split::pair_last_position;
+using split::pair_original_tiles;
+using split::pair_window_start;
 
 // Stage A of the producer: candidate logical row of slot `slot` in the cursor's tile.
 // Values read from the top-k array are returned unchecked (stage B range-checks them, so

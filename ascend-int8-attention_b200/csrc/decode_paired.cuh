@@ -22,9 +22,9 @@
 // unsplit too (attention.py:121-122: "Grouped-query kernel requires one KV partition").
 //
 // Shared memory: the 32-row query codes (16 KB a set) and the 32-column P codes do not fit beside
-// three 64 KB key tiles, so the key ring has two stages and the third stage's 64 KB hold them.  Two
-// stages are enough here: a tile now carries the work of two tokens, so fetching the next tile
-// takes longer than consuming this one less often than in decode_kernel.
+// three 64 KB key tiles, so the key ring has two stages and the third stage's 64 KB hold them.  The
+// price: at most two tiles are anywhere between their fetch and their O product, so the stages of a
+// tile overlap less with the next tile's than in decode_kernel.
 //
 // Query codes: a ring of three buffers.  An item needs one set of codes per cache kind it has tiles
 // of ("uses": original, then compressed); the n-th use of the CTA's life lives in buffer n mod 3,
@@ -61,14 +61,7 @@ __device__ __forceinline__ PairShape pair_shape(uint32_t batch_word, int32_t fir
     return s;
 }
 __device__ __forceinline__ PairShape pair_shape(const Item &it) { return pair_shape(it.batch, it.position, it.tile_end); }
-// May the query token at `position` see this key?  `row` is the logical row of the original cache
-// (kind 0) or the compressed row (kind 1).
-__device__ __forceinline__ bool pair_sees(int32_t position, uint32_t kind, uint32_t row)
-{
-    if (position < 0) return false;
-    const uint32_t pos = (uint32_t)position;
-    return kind == 0 ? (row <= pos && row + kWindow > pos) : row < (pos + 1u) / 128u;
-}
+using split::pair_sees;
 
 // ------------------------------------------------------------------ work split of the paired kernel
 // Groups, not tokens, are the unit: request b has ceil(tokens_b / 2) groups.  The flat cost list
@@ -121,12 +114,12 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
         return hi > lo ? (uint32_t)(hi - lo) : 0u;
     };
     uint32_t my_groups = 0;
-    for (uint32_t b = b_begin; b < b_end; ++b) my_groups += (tokens_of(b) + 1u) / 2u;
+    for (uint32_t b = b_begin; b < b_end; ++b) my_groups += split::pair_groups(tokens_of(b));
     uint32_t total_groups;
     uint32_t running = block_exclusive_scan(my_groups, sc->scan, total_groups);
     for (uint32_t b = b_begin; b < b_end; ++b) {
         sc->groups[b] = running;
-        running += (tokens_of(b) + 1u) / 2u;
+        running += split::pair_groups(tokens_of(b));
     }
     if (tid == 0) sc->groups[live_batch] = total_groups;
     __syncthreads();
@@ -147,7 +140,7 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
         d.token = t0;
         d.position = split::token_position(seq[b], sc->cu[b + 1], t0);
         d.batch_word = b | (tokens == 2u ? kPairBit : 0u);
-        d.tiles = pair_original_tiles(d.position, tokens) + (pair_compressed_rows(d.position, tokens) + kTileKeys - 1u) / kTileKeys;
+        d.tiles = split::pair_tiles(d.position, tokens);
         return d;
     };
     uint32_t my_cost = 0;
@@ -160,7 +153,7 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
     uint4 my_lo = make_uint4(0, 0, 0, 0), my_hi = my_lo;
     for (uint32_t g = g_begin; g < g_end; ++g) {
         const Group d = describe(g);
-        if (start / quota == me) {
+        if (split::pair_owner(start, quota) == me) {
             const uint4 lo = make_uint4(d.token, d.batch_word, (uint32_t)d.position, 0u);
             const uint4 hi = make_uint4(d.tiles, 0u, 1u, 0u);
             uint4 *dst = reinterpret_cast<uint4 *>(items + g);

@@ -116,5 +116,51 @@ SHAREDKV_HD uint32_t partial_slot(uint32_t first_cta, uint32_t part)
 // straddle the boundary behind its first CTA.
 SHAREDKV_HD uint32_t ticket_index(uint32_t first_cta) { return first_cta; }
 
+// ------------------------------------------------------------------ paired query tokens (C128)
+// The paired kernel walks two adjacent query tokens of a request as ONE item (reference.py:229-234,
+// 243-245 with query_group = 2): the original rows are the union of the two windows, tiled from the
+// union's first row; the compressed rows are the prefix of the later token.  `first_position` is
+// the position of the item's first token; an item has one token when the request's count is odd.
+constexpr uint32_t kWindowRows = 128;
+
+// Items of a request with `tokens` query tokens.
+SHAREDKV_HD uint32_t pair_groups(uint32_t tokens) { return (tokens + 1u) / 2u; }
+// Position of the item's last token (negative: no token of the item sees a key).
+SHAREDKV_HD int32_t pair_last_position(int32_t first_position, uint32_t tokens) { return first_position + (int32_t)tokens - 1; }
+// First row of the window union.
+SHAREDKV_HD uint32_t pair_window_start(int32_t first_position)
+{
+    return first_position >= (int32_t)kWindowRows ? (uint32_t)first_position + 1u - kWindowRows : 0u;
+}
+// 128-key tiles of the window union (1 or 2; 1 also when the item has no row at all, so that its
+// output rows are written).
+SHAREDKV_HD uint32_t pair_original_tiles(int32_t first_position, uint32_t tokens)
+{
+    const int32_t last = pair_last_position(first_position, tokens);
+    if (last < 0) return 1u;
+    const uint32_t rows = (uint32_t)last + 1u - pair_window_start(first_position);
+    return (rows + kTileKeys - 1u) / kTileKeys;
+}
+// Compressed rows an item walks: the prefix of its last token.
+SHAREDKV_HD uint32_t pair_compressed_rows(int32_t first_position, uint32_t tokens)
+{
+    const int32_t last = pair_last_position(first_position, tokens);
+    return last < 0 ? 0u : ((uint32_t)last + 1u) / 128u;
+}
+SHAREDKV_HD uint32_t pair_tiles(int32_t first_position, uint32_t tokens)
+{
+    return pair_original_tiles(first_position, tokens) + (pair_compressed_rows(first_position, tokens) + kTileKeys - 1u) / kTileKeys;
+}
+// May the query token at `position` see this key?  `row` is the logical row of the original cache
+// (kind 0) or the compressed row (kind 1).
+SHAREDKV_HD bool pair_sees(int32_t position, uint32_t kind, uint32_t row)
+{
+    if (position < 0) return false;
+    const uint32_t pos = (uint32_t)position;
+    return kind == 0 ? (row <= pos && row + kWindowRows > pos) : row < (pos + 1u) / 128u;
+}
+// An item is never split: it belongs to the CTA in whose cost range its first unit lies.
+SHAREDKV_HD uint32_t pair_owner(uint32_t cost_before, uint32_t quota) { return cost_before / quota; }
+
 }  // namespace split
 }  // namespace sharedkv

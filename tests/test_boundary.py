@@ -194,3 +194,21 @@ def test_work_split_invariants_on_the_host(tmp_path):
     done = subprocess.run([str(binary), "22000"], capture_output=True, text=True, timeout=600)
     assert done.returncode == 0, done.stderr
     assert "work split ok: 22000 workloads" in done.stdout
+
+
+def test_paired_work_split_invariants_on_the_host(tmp_path):
+    """The paired kernel's plan and tiling (csrc/work_split.h: pair_*) compiled for the host: every live
+    token in exactly one item of one or two adjacent tokens, a CTA's items consecutive, owners below
+    the grid, nobody more than one item over its quota, and the tiles of an item offering each token
+    exactly the rows it may see (reference.py:229-234,243-245 with query_group = 2)."""
+    import shutil
+    import subprocess
+    compiler = shutil.which("g++")
+    if compiler is None:
+        pytest.skip("no host C++ compiler")
+    binary = tmp_path / "test_pair_split"
+    subprocess.run([compiler, "-std=c++17", "-O2", "-I", str(ROOT / "ascend-int8-attention_b200" / "csrc"),
+                    str(ROOT / "tests" / "cpp" / "test_pair_split.cpp"), "-o", str(binary)], check=True)
+    done = subprocess.run([str(binary), "22000"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert "pair split ok: 22000 workloads" in done.stdout
