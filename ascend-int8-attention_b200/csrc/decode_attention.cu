@@ -201,7 +201,6 @@ struct PlanScratch {
     int32_t cu[kPlanStaged];
 };
 
-template <int RATIO>
 __device__ void plan_cta(const SharedKVArgs &p, const uint32_t grid, PlanScratch *sc, PlanResult *result)
 {
     const uint32_t tid = threadIdx.x;
@@ -985,7 +984,7 @@ __device__ void query_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, cons
     }
 }
 
-template <int RATIO, bool DEBUG>
+template <bool DEBUG>
 __device__ void softmax_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const Item *items,
                              const PlanResult &plan, uint32_t tmem)
 {
@@ -1139,7 +1138,7 @@ __device__ __forceinline__ float small_int_to_float(uint32_t x)
     return __fsub_rn(__uint_as_float(x + 0x4b400000u), 12582912.f);
 }
 
-template <int RATIO, bool DEBUG>
+template <bool DEBUG>
 __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg, const Shared &sm, const uint32_t live_tokens,
                                 const Item *items, const PlanResult &plan, uint32_t tmem)
 {
@@ -1316,7 +1315,7 @@ __device__ void accumulate_loop(const SharedKVArgs &p, const SharedKVDebug &dbg,
 }
 
 // ------------------------------------------------------------------ decode kernel
-template <int RATIO, bool DEBUG, bool TMA>
+template <bool DEBUG, bool TMA>
 __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs p, const SharedKVDebug dbg,
                                                              const __grid_constant__ CUtensorMap ori_map,
                                                              const __grid_constant__ CUtensorMap cmp_map,
@@ -1369,26 +1368,32 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel(const SharedKVArgs 
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
-    plan_cta<RATIO>(p, gridDim.x, reinterpret_cast<PlanScratch *>(sm.ptr + kSmKv), reinterpret_cast<PlanResult *>(sm.ptr + kSmPlan));
+    plan_cta(p, gridDim.x, reinterpret_cast<PlanScratch *>(sm.ptr + kSmKv), reinterpret_cast<PlanResult *>(sm.ptr + kSmPlan));
     const PlanResult &plan = *reinterpret_cast<const PlanResult *>(sm.ptr + kSmPlan);
 
     // Roles by warpgroup (four warps, one per SM sub-partition); the register file is re-divided
     // first: the groups that need few registers release them before the others grow.
     if (warp < 8) {
         if (kRegsSoftmax > kRegsLaunch) registers_acquire<kRegsSoftmax>();
-        softmax_loop<RATIO, DEBUG>(p, dbg, sm, items, plan, tmem);
+        softmax_loop<DEBUG>(p, dbg, sm, items, plan, tmem);
     } else if (warp < kWarpProducer) {
         registers_acquire<kRegsAccumulate>();
-        accumulate_loop<RATIO, DEBUG>(p, dbg, sm, plan.live_tokens, items, plan, tmem);
+        accumulate_loop<DEBUG>(p, dbg, sm, plan.live_tokens, items, plan, tmem);
     } else if (warp < kWarpMma || warp >= kWarpProducerB) {
         registers_release<kRegsProducer>();
         if (TMA && lane == 0) {
             tma_prefetch_descriptor(&ori_map);
-            tma_prefetch_descriptor(RATIO == 128 ? &cmp_page_map : &cmp_map);
+            tma_prefetch_descriptor(p.ratio == 4u ? &cmp_map : &cmp_page_map);
         }
         const uint32_t set = warp >= kWarpProducerB ? 1u : 0u;
-        producer_loop<RATIO, TMA, false>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map,
-                                         &cmp_page_map);
+        // One kernel function serves both layer kinds (a launch of ANOTHER kernel function costs about
+        // 4 us more than a launch of the same one, measured on alternating C4 / C128 layers); the
+        // producers, the only role whose code depends on the kind, exist once per kind.  Ratio 1
+        // (no compressed cache) takes the ratio-128 producers and never reaches a compressed tile.
+        if (p.ratio == 4u)
+            producer_loop<4, TMA, false>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map, &cmp_page_map);
+        else
+            producer_loop<128, TMA, false>(p, sm, items, plan, set, (warp - kWarpProducer) & 3u, lane, &ori_map, &cmp_map, &cmp_page_map);
         cp_async_wait<0>();
     } else {
         if (kRegsIssue < kRegsLaunch) registers_release<kRegsIssue>();
@@ -1493,7 +1498,7 @@ const MapSet *tensor_maps(uint64_t ori, uint64_t cmp, uint64_t cmp_stride, bool 
     return &e;
 }
 
-template <int RATIO, bool DEBUG, bool TMA>
+template <bool DEBUG, bool TMA>
 cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const CUtensorMap &ori_map,
                           const CUtensorMap &cmp_map, const CUtensorMap &cmp_page_map, uint32_t grid,
                           cudaStream_t stream, int device)
@@ -1503,7 +1508,7 @@ cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const C
     const bool cached = device >= 0 && device < kMaxDevices;
     const uint64_t bit = cached ? 1ull << device : 0ull;
     if (!cached || !(configured.load(std::memory_order_relaxed) & bit)) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel<RATIO, DEBUG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(decode_kernel<DEBUG, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kSmemBytes);
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_relaxed);
@@ -1518,10 +1523,9 @@ cudaError_t launch_decode(const SharedKVArgs &a, const SharedKVDebug &d, const C
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = programmatic_launch_enabled() ? 1u : 0u;
-    return cudaLaunchKernelEx(&config, decode_kernel<RATIO, DEBUG, TMA>, a, d, ori_map, cmp_map, cmp_page_map);
+    return cudaLaunchKernelEx(&config, decode_kernel<DEBUG, TMA>, a, d, ori_map, cmp_map, cmp_page_map);
 }
 
-template <int RATIO>
 int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debug, int sms)
 {
     uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
@@ -1535,23 +1539,23 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
     static const CUtensorMap no_map = {};
     bool tma = a.oriStride % kDim == 0 && a.cmpStride % kDim == 0 && !(debug && (debug->reserved & kDebugLegacyGather)) &&
                (uint64_t)a.oriPages * (a.oriStride / kDim) < (uint64_t)kRowsInMap && a.cmpStride / kDim < 65536;
-    const MapSet *maps = tma ? tensor_maps(a.ori, a.cmp, a.cmpStride, RATIO == 128) : nullptr;
+    const MapSet *maps = tma ? tensor_maps(a.ori, a.cmp, a.cmpStride, a.ratio != 4u) : nullptr;
     if (maps == nullptr) tma = false;
     const CUtensorMap &ori_map = tma ? maps->ori_map : no_map, &cmp_map = tma ? maps->cmp_map : no_map,
                       &cmp_page_map = tma ? maps->cmp_page_map : no_map;
     SharedKVDebug d = {};
     if (debug) {
         d = *debug;
-        e = tma ? launch_decode<RATIO, true, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
-                : launch_decode<RATIO, true, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
+        e = tma ? launch_decode<true, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+                : launch_decode<true, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
     } else {
-        e = tma ? launch_decode<RATIO, false, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
-                : launch_decode<RATIO, false, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
+        e = tma ? launch_decode<false, true>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+                : launch_decode<false, false>(a, d, ori_map, cmp_map, cmp_page_map, grid, stream, device);
     }
     return (int)e;
 }
 
-// Paired-query C128 launch (decode_paired.cuh): same grid, block and tensor maps as launch<128>.
+// Paired-query C128 launch (decode_paired.cuh): same grid, block and tensor maps as launch() of a ratio-128 layer.
 template <bool TMA>
 cudaError_t launch_decode_paired(const SharedKVArgs &a, const CUtensorMap &ori_map, const CUtensorMap &cmp_map,
                                  const CUtensorMap &cmp_page_map, uint32_t grid, cudaStream_t stream, int device)
@@ -1647,7 +1651,7 @@ int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, c
     const int sms = device_sm_count();
     if (sms <= 0) return (int)cudaErrorInvalidDevice;
     if (paired) return launch_paired(a, stream, sms);
-    return ratio == 4 ? launch<4>(a, stream, debug, sms) : launch<128>(a, stream, debug, sms);
+    return launch(a, stream, debug, sms);
 }
 
 }  // namespace sharedkv

@@ -817,8 +817,8 @@ def main():
         "per_gpu_value": value / world, "kv_gbs": kv_gbs, "kv_gbs_per_gpu": kv_gbs / world,
         "burst": {"value": burst_counts[0] / (burst_total_ms / 1000), "ms_per_pass": burst_total_ms / args.steps, "passes": args.steps,
                   "clocks": clock_note(burst_clocks, burst_total_ms / args.steps)},
-        "roofline": dict(roof[dominant], kernel=f"decode_kernel<{dominant}>"),
-        "roofline_other": {f"decode_kernel<{r}>": v for r, v in roof.items() if r != dominant},
+        "roofline": dict(roof[dominant], kernel=f"decode_kernel on C{dominant} layers"),
+        "roofline_other": {f"decode_kernel on C{r} layers": v for r, v in roof.items() if r != dominant},
         "writer": writer,
         "cpu_baseline": None if not cpu_n else {
             "value": cpu_qps, "unit": "queries/s", "cores": os.cpu_count() or 1, "kind": cpu_kind,
