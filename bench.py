@@ -55,7 +55,7 @@ ROW_BYTES = 512
 # DRAM traffic (read + written) per algorithmic KV byte, from profiler captures of smaller launches
 # of the same kernels (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of
 # the captured launch); traffic grows in proportion to the queries processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.078, 128: 1.040}
+TRAFFIC_PER_ALGORITHMIC_BYTE = {4: 1.075, 128: 1.040}
 
 
 def measured_peaks():
