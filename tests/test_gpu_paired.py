@@ -102,6 +102,55 @@ def test_chunked_prefill_chunk_with_a_dead_request():
     assert not out[81:].any() and not op.lse[81:].any()
 
 
+def test_graph_replay_and_a_workspace_shared_with_the_one_token_kernel():
+    """A captured graph that launches the one-token kernel and the paired kernel in turn on ONE
+    workspace (a serving scratch pool hands the same buffer to launches of different plans): the
+    paired launch leaves the split-K tickets of the workspace as it found them, and replays give the
+    bits of the first run."""
+    import ctypes
+    from npu_sparse_attn_sharedkv_int8 import c8_attention
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    case, ori_scale, cmp_scale, z = load_case("grouped_c128")
+    dev = to_device(case, DEVICE)
+    shared = torch.empty(c8_attention.workspace_bytes(case.q.shape[0]) + 256, dtype=torch.uint8, device=DEVICE)
+    shared = shared[(-shared.data_ptr()) % 256:][:c8_attention.workspace_bytes(case.q.shape[0])]
+    pool = lambda name, shape, dtype, device: shared
+    single = PreparedAttention(dev, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), return_lse=True, scratch_allocator=pool)
+    paired = prepared(dev, ori_scale, cmp_scale, scratch_allocator=pool)
+    assert single.workspace.data_ptr() == paired.workspace.data_ptr()
+    for op in (single, paired, single, paired):
+        op.run()
+    torch.cuda.synchronize()
+    first = single.out.clone(), paired.out.clone(), paired.lse.clone()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream(device=DEVICE)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for op in (paired, single, paired, single):
+                op.run()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        single.out.fill_(1.0)
+        paired.out.fill_(1.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(single.out, first[0]) and torch.equal(paired.out, first[1]) and torch.equal(paired.lse, first[2])
+    c8_attention.workspace_status(paired)
+    assert_device_band(paired.out.cpu(), paired.lse.cpu(), bf16(z["out_g2"]), torch.from_numpy(z["lse_g2"]))
+
+    # the workspace-free entry takes the paired variant as well
+    from npu_sparse_attn_sharedkv_int8 import runtime
+    static_scratch = runtime._library().sharedkv_attention_static_scratch
+    static_scratch.argtypes, static_scratch.restype = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p], ctypes.c_int
+    out = torch.full_like(paired.out, 7.0)
+    args = type(paired.args).from_buffer_copy(paired.args)
+    args.out, args.lse, args.workspace = out.data_ptr(), 0, 0
+    runtime.check(static_scratch(7, runtime.current_stream(0), ctypes.byref(args)), "static-scratch launch")
+    torch.cuda.synchronize()
+    assert torch.equal(out, first[1])
+
+
 def test_selection_rules():
     case, ori_scale, cmp_scale, _ = load_case("grouped_c4")
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
