@@ -528,7 +528,7 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
             return row <= (uint32_t)last ? (int32_t)row : -1;
         }
         const uint32_t s = (c.j - windows) * kTileKeys + slot;
-        return s < pair_compressed_rows(it.position, tokens) ? (int32_t)s : -1;
+        return s < pair_compressed_rows(it.position, tokens, p.ratio) ? (int32_t)s : -1;
     }
     if (it.position < 0) return -1;
     if (c.j < ori_tiles) {
@@ -635,7 +635,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
                 const int32_t c = cand[u];
                 if (GROUP) {
                     // the compressed prefix is that of the group's last token
-                    const uint32_t limit = ori ? 0x7fffffffu : pair_compressed_rows(cb.position, pair_tokens(cb.batch));
+                    const uint32_t limit = ori ? 0x7fffffffu : pair_compressed_rows(cb.position, pair_tokens(cb.batch), p.ratio);
                     const uint32_t request = pair_batch(cb.batch);
                     if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
                         off_b = (c & 31) | (ori ? 256 : 0);
@@ -1609,21 +1609,22 @@ int workspace_status(const void *workspace, cudaStream_t stream)
                                     cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return (int)e;
-    return status == kStatusOk ? SHAREDKV_OK : SHAREDKV_ETIMEDOUT;
+    return status == kStatusOk ? SHAREDKV_OK : status == kStatusRange ? SHAREDKV_ERANGE : SHAREDKV_ETIMEDOUT;
 }
 
 int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, const SharedKVDebug *debug)
 {
     if (args == nullptr) return SHAREDKV_EINVAL;
-    const bool general = variant == SHAREDKV_VARIANT_GENERAL, paired = variant == SHAREDKV_VARIANT_PAIRED;
+    const bool general = variant == SHAREDKV_VARIANT_GENERAL;
+    const bool paired = variant == SHAREDKV_VARIANT_PAIRED || variant == SHAREDKV_VARIANT_PAIRED_SPARSE;
     if (!general && !paired && variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
         return SHAREDKV_EVARIANT;
     SharedKVArgs a = *args;
     if (a.tokens == 0 || a.batch == 0) return SHAREDKV_OK;
     // The C4 / C128 entries take their own ratio and no explicit original slots, as the reference's
     // do; the general entry takes ratio 1 (no compressed cache), 4 or 128, with or without them.
-    // The paired entry is the C128 arithmetic with two adjacent query tokens of a request per work item.
-    const uint32_t ratio = general ? a.ratio : ((variant == SHAREDKV_VARIANT_C128 || paired) ? 128u : 4u);
+    // The paired entries are the C128 arithmetic, and the grouped C4 walk, with two adjacent query tokens of a request per work item.
+    const uint32_t ratio = general ? a.ratio : ((variant == SHAREDKV_VARIANT_C128 || variant == SHAREDKV_VARIANT_PAIRED) ? 128u : 4u);
     if (paired && (debug != nullptr || a.batch + 1u > kPlanStaged)) return SHAREDKV_EINVAL;
     if (a.ratio != ratio || (ratio != 1u && ratio != 4u && ratio != 128u) || (!general && a.oriIndices != 0)) return SHAREDKV_EINVAL;
     if (a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage) return SHAREDKV_EINVAL;

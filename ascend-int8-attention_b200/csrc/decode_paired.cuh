@@ -14,8 +14,13 @@
 // reference.py:229-234,243-245): the original rows of an item are the union of its tokens' windows,
 // tiled from the union's first row, each token masking the rows outside its own window; the
 // compressed rows are the prefix of the later token, the earlier token masking what it may not see.
-// Ratio 128 only (a grouped C4 token walks all compressed rows with a multiplicity bias: another
-// algorithm, :246-249), no explicit original slots (the reference refuses them with groups too).
+// Ratio 128, or ratio 4 as the reference groups it (:246-249,300-301): a grouped C4 token does not
+// gather its top-k rows but walks ALL compressed rows of the pair's later token; a row counts as
+// often as the token's own top-k list names it (log(multiplicity) is added to its logits) and rows
+// the list does not name are masked.  The query warp of the compressed kind counts the names into
+// a table in shared memory; the bound the reference puts on such plans (contexts of at most 1024
+// tokens, attention.py:89-98) makes that table 256 rows per token.  No explicit original slots (the
+// reference refuses them with groups too).
 //
 // Items are not split between CTAs: an item belongs to the CTA in whose share of the cost list it
 // begins, so there are no partial states and no merges.  The reference's grouped plans are
@@ -39,7 +44,9 @@ constexpr uint32_t kSmP2 = kSmQ2 + 3 * 16384;                 // 2 buffers x [2 
 constexpr uint32_t kSmRed2 = kSmP2 + 2 * 4096;                // FP32 [2 halves][2 parities][2 tokens][4 warps][4]
 constexpr uint32_t kSmAlpha2 = kSmRed2 + 512;                 // FP32 [8 items][2 tokens][2 kinds][8]: alpha * softmax_scale
 constexpr uint32_t kSmFinal2 = kSmAlpha2 + 8 * 128;           // FP32 [8 items][2 tokens][16]: m[8], l[8]
-static_assert(kSmFinal2 + 8 * 128 <= kStages * kTileBytes, "the paired kernel's extras live inside the third key tile");
+constexpr uint32_t kSmMult2 = kSmFinal2 + 8 * 128;            // UINT32 [2 items][2 tokens][256 rows]: grouped C4 multiplicities
+constexpr uint32_t kPairSparseRows = split::kPairSparseRows;
+static_assert(kSmMult2 + 2 * 2 * kPairSparseRows * 4 <= kStages * kTileBytes, "the paired kernel's extras live inside the third key tile");
 // tensor memory: S[b] at 32 b (32 columns), O[b] at 64 + 128 b as four 32-column channel blocks
 constexpr uint32_t kTmemCols2 = 512;
 constexpr uint32_t kColS2 = 0, kColO2 = 64;
@@ -140,7 +147,7 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
         d.token = t0;
         d.position = split::token_position(seq[b], sc->cu[b + 1], t0);
         d.batch_word = b | (tokens == 2u ? kPairBit : 0u);
-        d.tiles = split::pair_tiles(d.position, tokens);
+        d.tiles = split::pair_tiles(d.position, tokens, p.ratio);
         return d;
     };
     uint32_t my_cost = 0;
@@ -270,6 +277,28 @@ __device__ void pair_query_loop(const SharedKVArgs &p, const Shared &sm, const I
             // the use that had the buffer before must no longer be read
             if (round > 0 && !wait_phase<3>(sm, kBarQFree + buf, (round - 1u) & 1u)) return;
             if (use_kind == kind) {
+                if (kind == 1 && p.ratio == 4u) {
+                    // grouped C4: how often each token's top-k list names each compressed row.  The table
+                    // slot was last read for item k - 2, which the softmax warps have finished by now.
+                    if (k >= 2 && !wait_phase<3>(sm, kBarItemDone + ((k - 2u) & 7u), ((k - 2u) >> 3) & 1u)) return;
+                    uint32_t *table = reinterpret_cast<uint32_t *>(sm.ptr + kSmMult2) + (k & 1u) * 2u * kPairSparseRows;
+                    for (uint32_t i = lane; i < 2u * kPairSparseRows; i += 32u) table[i] = 0u;
+                    __syncwarp();
+                    bool beyond = false;
+                    for (uint32_t token = 0; token < shape.tokens; ++token) {
+                        const int32_t position = it.position + (int32_t)token;
+                        const uint32_t count = position < 0 ? 0u : ((uint32_t)position + 1u) / 4u;
+                        beyond |= count > kPairSparseRows;
+                        const int32_t *ix = reinterpret_cast<const int32_t *>(p.indices) + (uint64_t)(it.token + token) * p.topk;
+                        for (uint32_t i = lane; i < p.topk; i += 32u) {
+                            const int32_t v = ix[i];
+                            if (v >= 0 && (uint32_t)v < count && (uint32_t)v < kPairSparseRows) atomicAdd(table + token * kPairSparseRows + (uint32_t)v, 1u);
+                        }
+                    }
+                    // a context beyond the table is outside this entry's contract: the launch is marked as failed
+                    if (beyond && lane == 0) reinterpret_cast<PlanHeader *>(reinterpret_cast<char *>(p.workspace))->status = kStatusRange;
+                    __syncwarp();
+                }
                 // rows of a token the item does not have keep whatever they held: their S columns are never read
                 for (uint32_t token = 0; token < shape.tokens; ++token) {
                     float *alphas = reinterpret_cast<float *>(sm.ptr + kSmAlpha2) + ((k & 7u) * 2u + token) * 16u + kind * 8u;
@@ -420,8 +449,18 @@ __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const
             const bool has_key = (mask_word >> lane) & 1u;
             // what this key is to each token: a window row (logical row number) or a compressed row
             const uint32_t row = kind == 0 ? start + j * kTileKeys + key : (j - shape.windows) * kTileKeys + key;
-            const bool valid0 = has_key && pair_sees(it.position, kind, row);
-            const bool valid1 = has_key && shape.tokens == 2u && pair_sees(it.position + 1, kind, row);
+            bool valid0 = has_key && pair_sees(it.position, kind, row, p.ratio);
+            bool valid1 = has_key && shape.tokens == 2u && pair_sees(it.position + 1, kind, row, p.ratio);
+            float bias0 = 0.f, bias1 = 0.f;
+            if (kind == 1u && p.ratio == 4u) {
+                // grouped C4: the token's own top-k list decides, and a row named n times counts n times
+                const uint32_t *mult = reinterpret_cast<const uint32_t *>(sm.ptr + kSmMult2) + (k & 1u) * 2u * kPairSparseRows;
+                const uint32_t n0 = row < kPairSparseRows ? mult[row] : 0u, n1 = row < kPairSparseRows ? mult[kPairSparseRows + row] : 0u;
+                valid0 = valid0 && n0 > 0u;
+                valid1 = valid1 && n1 > 0u;
+                bias0 = logf((float)max(n0, 1u));
+                bias1 = logf((float)max(n1, 1u));
+            }
             if (!wait_phase<0>(sm, kBarSFull + buf, ph)) return;
             tc_fence_after();
             uint32_t a_hi[4], a_lo[4], b_hi[4], b_lo[4];
@@ -438,8 +477,8 @@ __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const
             for (int i = 0; i < 4; ++i) {
                 const float d0 = __fadd_rn((float)(int)a_hi[i], __fmul_rn((float)(int)a_lo[i], kInv127));
                 const float d1 = __fadd_rn((float)(int)b_hi[i], __fmul_rn((float)(int)b_lo[i], kInv127));
-                logit0[i] = valid0 ? __fmul_rn(d0, alphas[kind * 8u + half * 4u + i]) : kMasked;
-                logit1[i] = valid1 ? __fmul_rn(d1, alphas[16u + kind * 8u + half * 4u + i]) : kMasked;
+                logit0[i] = valid0 ? __fadd_rn(__fmul_rn(d0, alphas[kind * 8u + half * 4u + i]), bias0) : kMasked;
+                logit1[i] = valid1 ? __fadd_rn(__fmul_rn(d1, alphas[16u + kind * 8u + half * 4u + i]), bias1) : kMasked;
             }
             const float wmax0 = warp_reduce4<true>(logit0, lane), wmax1 = warp_reduce4<true>(logit1, lane);
             float *slot_red = red + (t & 1u) * 32u;

@@ -38,7 +38,7 @@ __host__ __device__ constexpr uint64_t ws_bytes(uint32_t tokens)
     return ws_partials(tokens) + (uint64_t)split::kMaxCtas * 2ull * kPartialFloats * 4ull;
 }
 
-enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1 };
+enum : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusRange = 2 };      // status word of a workspace (sticky)
 
 // SM count of the current device, cached per ordinal; <= 0 on failure.
 int device_sm_count();

@@ -141,24 +141,30 @@ SHAREDKV_HD uint32_t pair_original_tiles(int32_t first_position, uint32_t tokens
     const uint32_t rows = (uint32_t)last + 1u - pair_window_start(first_position);
     return (rows + kTileKeys - 1u) / kTileKeys;
 }
-// Compressed rows an item walks: the prefix of its last token.
-SHAREDKV_HD uint32_t pair_compressed_rows(int32_t first_position, uint32_t tokens)
+// Compressed rows an item walks: the prefix of its last token, `ratio` = 128, or 4 for the grouped
+// C4 walk, in which a token attends every compressed row its own top-k list names, weighted by how
+// often it names it (reference.py:246-249,300-301).
+SHAREDKV_HD uint32_t pair_compressed_rows(int32_t first_position, uint32_t tokens, uint32_t ratio)
 {
     const int32_t last = pair_last_position(first_position, tokens);
-    return last < 0 ? 0u : ((uint32_t)last + 1u) / 128u;
+    return last < 0 ? 0u : ((uint32_t)last + 1u) / ratio;
 }
-SHAREDKV_HD uint32_t pair_tiles(int32_t first_position, uint32_t tokens)
+SHAREDKV_HD uint32_t pair_tiles(int32_t first_position, uint32_t tokens, uint32_t ratio)
 {
-    return pair_original_tiles(first_position, tokens) + (pair_compressed_rows(first_position, tokens) + kTileKeys - 1u) / kTileKeys;
+    return pair_original_tiles(first_position, tokens) + (pair_compressed_rows(first_position, tokens, ratio) + kTileKeys - 1u) / kTileKeys;
 }
 // May the query token at `position` see this key?  `row` is the logical row of the original cache
-// (kind 0) or the compressed row (kind 1).
-SHAREDKV_HD bool pair_sees(int32_t position, uint32_t kind, uint32_t row)
+// (kind 0) or the compressed row (kind 1; for the grouped C4 walk the token's top-k list decides
+// on top of this).
+SHAREDKV_HD bool pair_sees(int32_t position, uint32_t kind, uint32_t row, uint32_t ratio)
 {
     if (position < 0) return false;
     const uint32_t pos = (uint32_t)position;
-    return kind == 0 ? (row <= pos && row + kWindowRows > pos) : row < (pos + 1u) / 128u;
+    return kind == 0 ? (row <= pos && row + kWindowRows > pos) : row < (pos + 1u) / ratio;
 }
+// Rows of the compressed cache the grouped C4 walk keeps multiplicities for (contexts of at most
+// 1024 tokens, the bound the reference puts on its grouped C4 plans, attention.py:89-98).
+constexpr uint32_t kPairSparseRows = 256;
 // An item is never split: it belongs to the CTA in whose cost range its first unit lies.
 SHAREDKV_HD uint32_t pair_owner(uint32_t cost_before, uint32_t quota) { return cost_before / quota; }
 

@@ -105,8 +105,11 @@ class PreparedAttention:
         # selects the paired-query C128 kernel: two adjacent tokens of a request share their tiles.
         _require(tile_size in (None, 128), "The CUDA kernels use 128-key tiles; tile_size must be None or 128")
         _require(query_group in (None, 1, 2), "The CUDA kernels take one or two query tokens per task; query_group must be None, 1 or 2")
-        _require(query_group != 2 or (heads == 8 and case.ratio == 128),
-                 "Query grouping requires eight heads and a ratio-128 layer")
+        # grouped C4 walks every compressed row of a context, so it is for short contexts only (attention.py:89-98)
+        short_c4 = (case.ratio == 4 and isinstance(max_seq_len, int) and 0 < max_seq_len <= 1024
+                    and case.cmp_indices is not None and case.cmp_indices.shape[-1] <= 1024)
+        _require(query_group != 2 or (heads == 8 and (case.ratio == 128 or short_c4)),
+                 "Query grouping requires eight heads; C4 also requires a max_seq_len bound <= 1024 and top-k <= 1024")
         _require(query_group != 2 or case.ori_indices is None, "Explicit original slots require ungrouped queries")
         _require(splits is None or (isinstance(splits, int) and 1 <= splits <= 24), "Expected 1..24 KV partitions")
         _require(not (adaptive_splits or trim_cube_tails or dynamic_grouped_c128),
@@ -114,7 +117,7 @@ class PreparedAttention:
         self.query_group, self.tile_size, self.splits = query_group or 1, 128, 1
         self.adaptive_splits = self.trim_cube_tails = self.dynamic_grouped_c128 = False
         general = case.ratio == 1 or case.ori_indices is not None      # the reference's compatibility entry (variant 0)
-        self.dynamic_c4 = case.ratio == 4 and not general
+        self.dynamic_c4 = case.ratio == 4 and not general and self.query_group == 1
         self.dynamic_c128 = case.ratio == 128 and not general and self.query_group == 1
         _require(max_seq_len is None or (isinstance(max_seq_len, int) and max_seq_len > 0
                                          and (case.ori_indices is not None

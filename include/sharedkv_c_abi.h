@@ -102,9 +102,9 @@ enum {
 };
 
 /* Kernel variants of the host bridge: 0 is the reference's general 128-key-tile kernel
- * (launch.cpp:33), 7 its paired-query C128 kernel (launch.cpp:40), 20-22 its C4 / C128 decode
+ * (launch.cpp:33), 7 and 8 its paired-query C128 and C4 kernels (launch.cpp:40-41), 20-22 its C4 / C128 decode
  * kernels (c8_launch.cpp:12-18). */
-enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_PAIRED = 7, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
+enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_PAIRED = 7, SHAREDKV_VARIANT_PAIRED_SPARSE = 8, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
 
 /* sizeof(SharedKVArgs) / sizeof(CacheWriteArgs) as compiled into the library; the
  * Python layer compares them with its ctypes mirrors (attention.py:223-226,
@@ -133,7 +133,8 @@ SHAREDKV_API int sharedkv_workspace_init(void *workspace, void *stream);
  * product, another warp) is bounded; when one runs out, the thread block gives up, frees its
  * tensor memory, and sets a status word in the workspace that stays set until the workspace is
  * initialised again.  This call synchronises `stream`, reads the word and returns SHAREDKV_OK,
- * SHAREDKV_ETIMEDOUT (the outputs of some launch that used this workspace are invalid) or a
+ * SHAREDKV_ETIMEDOUT (the outputs of some launch that used this workspace are invalid),
+ * SHAREDKV_ERANGE (a launch_sharedkv_paired_sparse launch met a context beyond its bound) or a
  * cudaError_t.  It is a diagnostic: nothing on the launch path calls it.  The reference reports
  * device failures through its runtime's stream errors instead. */
 SHAREDKV_API int sharedkv_workspace_status(const void *workspace, void *stream);
@@ -153,6 +154,14 @@ SHAREDKV_API int launch_sharedkv(uint32_t blocks, void *stream, const SharedKVAr
  * union of the two windows.  No explicit original slots; batch < 11776.  Replaces
  * csrc/kernels/sharedkv_paired.cpp:7 (`launch_sharedkv_paired`, variant 7 of launch.cpp:40). */
 SHAREDKV_API int launch_sharedkv_paired(uint32_t blocks, void *stream, const SharedKVArgs *args);
+/* Paired queries on a ratio-4 layer, as the reference groups C4 (reference.py:246-249,300-301): a token
+ * attends every compressed row of the pair's later token that its own top-k list (args->indices,
+ * topk <= 1024) names, a row named n times with log(n) added to its logits.  Contexts of at most
+ * 1024 tokens (the reference's bound on grouped C4 plans, attention.py:89-98); a longer context sets
+ * the workspace status to SHAREDKV_ERANGE (sharedkv_workspace_status) and its rows past the 256th
+ * compressed row are not attended.  Replaces csrc/kernels/sharedkv_paired_sparse.cpp:7
+ * (`launch_sharedkv_paired_sparse`, variant 8 of launch.cpp:41). */
+SHAREDKV_API int launch_sharedkv_paired_sparse(uint32_t blocks, void *stream, const SharedKVArgs *args);
 
 /* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
  * query token.  `blocks` is accepted for signature compatibility and ignored: the

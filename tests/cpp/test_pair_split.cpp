@@ -20,7 +20,7 @@ using namespace sharedkv::split;
 #define REQUIRE(cond)                                                                                            \
     do {                                                                                                         \
         if (!(cond)) {                                                                                           \
-            std::fprintf(stderr, "workload %u (grid %u, batch %u): %s failed at line %d\n", trial, grid, batch, #cond, __LINE__); \
+            std::fprintf(stderr, "workload %u (ratio %u, grid %u, batch %u): %s failed at line %d\n", trial, ratio, grid, batch, #cond, __LINE__); \
             return 1;                                                                                            \
         }                                                                                                        \
     } while (0)
@@ -33,10 +33,11 @@ int main(int argc, char **argv)
     unsigned long long items_seen = 0, single_items = 0, two_window_tiles = 0;
     for (unsigned trial = 0; trial < workloads; ++trial) {
         const uint32_t grid = trial % 7 == 0 ? uniform(1, 4) : uniform(1, kMaxCtas);
+        const uint32_t ratio = trial % 3 == 2 ? 4u : 128u;          // 4: the grouped C4 walk over a short context
         const uint32_t shape = rng() % 8;
         const uint32_t batch = shape == 0 ? uniform(1, 3000) : shape < 4 ? uniform(1, 8) : uniform(1, 200);
         const uint32_t max_queries = shape == 0 ? 3 : (rng() % 3 == 0 ? 600 : 9);
-        const uint32_t max_context = rng() % 3 == 0 ? (1u << 20) : (rng() % 2 ? 135000u : 300u);
+        const uint32_t max_context = ratio == 4u ? 1024u : rng() % 3 == 0 ? (1u << 20) : (rng() % 2 ? 135000u : 300u);
         std::vector<int32_t> cu(batch + 1, 0), seq(batch, 0);
         for (uint32_t b = 0; b < batch; ++b) {
             const uint32_t queries = uniform(1, max_queries);
@@ -63,7 +64,7 @@ int main(int argc, char **argv)
                 d.token = (uint32_t)cu[b] + 2u * g;
                 d.tokens = std::min(2u, (uint32_t)cu[b + 1] - d.token);
                 d.position = token_position(seq[b], cu[b + 1], d.token);
-                d.tiles = pair_tiles(d.position, d.tokens);
+                d.tiles = pair_tiles(d.position, d.tokens, ratio);
                 groups.push_back(d);
             }
         }
@@ -104,7 +105,7 @@ int main(int argc, char **argv)
             two_window_tiles += windows == 2;
             const uint32_t start = pair_window_start(d.position);
             const int32_t last = pair_last_position(d.position, d.tokens);
-            const uint32_t compressed = pair_compressed_rows(d.position, d.tokens);
+            const uint32_t compressed = pair_compressed_rows(d.position, d.tokens, ratio);
             REQUIRE(d.tiles == windows + (compressed + kTileKeys - 1) / kTileKeys);
             for (uint32_t i = 0; i < d.tokens; ++i) {
                 const int32_t position = d.position + (int32_t)i;
@@ -113,17 +114,17 @@ int main(int argc, char **argv)
                 for (uint32_t slot = 0; slot < windows * kTileKeys; ++slot) {
                     const uint32_t row = start + slot;
                     const bool offered = last >= 0 && row <= (uint32_t)last;          // the producer fetches it
-                    if (offered && pair_sees(position, 0, row)) ++seen;
-                    if (pair_sees(position, 0, row)) REQUIRE(offered);
+                    if (offered && pair_sees(position, 0, row, ratio)) ++seen;
+                    if (pair_sees(position, 0, row, ratio)) REQUIRE(offered);
                 }
                 const uint32_t expect = position < 0 ? 0u : std::min((uint32_t)position + 1u, kWindowRows);
                 REQUIRE(seen == expect);
                 if (position >= 0) REQUIRE(start <= (uint32_t)std::max(0, position - 127));      // nothing the token needs lies in front of the union
                 // compressed rows: the token's own prefix, inside the item's
-                const uint32_t own = position < 0 ? 0u : ((uint32_t)position + 1u) / 128u;
+                const uint32_t own = position < 0 ? 0u : ((uint32_t)position + 1u) / ratio;
                 REQUIRE(own <= compressed);
-                if (own) REQUIRE(pair_sees(position, 1, own - 1));
-                REQUIRE(!pair_sees(position, 1, own));
+                if (own) REQUIRE(pair_sees(position, 1, own - 1, ratio));
+                REQUIRE(!pair_sees(position, 1, own, ratio));
             }
             ++items_seen;
         }

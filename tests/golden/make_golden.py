@@ -200,9 +200,13 @@ def grouped_golden(ref):
     """grouped_c128.npz / grouped_c4.npz: `tiled_quantized_reference(..., query_group=2 / 4)` on chunked-prefill
     shapes (several query tokens per request), reference.py:229-234,243-249,300-301."""
     for name, ratio, queries, lengths, seed in (('grouped_c128', 128, [5, 2, 1], [16500, 40000, 300], 31),
-                                                ('grouped_c4', 4, [4, 3], [700, 2051], 32)):
+                                                ('grouped_c4', 4, [4, 3], [700, 2051], 32),
+                                                # contexts within the reference's bound on grouped C4 plans (attention.py:89-98)
+                                                ('grouped_c4_short', 4, [5, 2, 3, 1], [700, 1024, 131, 9], 33)):
         def duplicate(indices, g):
             indices[:, :, 40:60] = indices[:, :, 0:20]             # duplicates: multiplicity 2
+            if name == 'grouped_c4_short':
+                indices[:, :, 100:110] = indices[:, :, 0:10]       # and 3
         case, oq, cq = windowed_case(ref, ratio=ratio, queries=queries, lengths=lengths, seed=seed,
                                      edit_indices=duplicate if ratio == 4 else None)
         arrays = dict(q=bits(case.q), ori=case.ori.numpy(), ori_table=case.ori_block_table.numpy(), cmp=case.cmp.numpy(),

@@ -10,7 +10,7 @@ from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, SharedKVC
 GOLDEN = Path(__file__).resolve().parent / "golden"
 ATTENTION_CASES = ("unit_c4", "unit_c128", "config0_c4", "holes_c4", "short_c4", "mixed_c128", "real_c4", "real_c128")
 SLOT_CASES = ("slots_swa", "slots_c4")       # explicit original slots: a ratio-1 layer and a C4 layer
-GROUPED_CASES = ("grouped_c128", "grouped_c4")      # several query tokens per request; outputs for query_group 1, 2 and 4
+GROUPED_CASES = ("grouped_c128", "grouped_c4", "grouped_c4_short")      # several query tokens per request; outputs for query_group 1, 2 and 4
 PAGE_STRIDE = 622592          # the non-unit page stride the reference's device tests use (tests/support/serving_shapes.py:19)
 
 

@@ -1,10 +1,12 @@
-"""Paired-query C128 kernel (query_group = 2) on the GPU against the reference's grouped arithmetic.
+"""Paired-query kernel (query_group = 2) on the GPU against the reference's grouped arithmetic.
 
-The reference's tiled oracle with query_group = 2 (reference.py:229-234,243-245) tiles the union of
-two adjacent tokens' windows from its first row and walks the later token's compressed prefix; the
-paired kernel follows that tiling and never splits an item, so its results are held to the
-reference's own device band (rtol 0.008, atol 0.0003 on BF16 output, 2e-5 on LSE; reference
-tests/npu/test_attention.py:102-103) against the golden `out_g2` and against the oracle.
+The reference's tiled oracle with query_group = 2 (reference.py:229-234,243-249,300-301) tiles the
+union of two adjacent tokens' windows from its first row and walks the later token's compressed
+prefix; on a ratio-4 layer every token attends the rows its own top-k list names, a row named n
+times with log(n) added to its logits.  The paired kernel follows that tiling and never splits an
+item, so its results are held to the reference's own device band (rtol 0.008, atol 0.0003 on BF16
+output, 2e-5 on LSE; reference tests/npu/test_attention.py:102-103) against the golden `out_g2` and
+against the oracle.
 """
 from dataclasses import replace
 import math
@@ -102,6 +104,77 @@ def test_chunked_prefill_chunk_with_a_dead_request():
     assert not out[81:].any() and not op.lse[81:].any()
 
 
+def test_golden_grouped_c4_case_with_duplicate_selections():
+    """Contexts of 700, 1024, 131 and 9 tokens, 5 + 2 + 3 + 1 query tokens, top-k lists that name some
+    rows two and three times (and so drop others)."""
+    case, ori_scale, cmp_scale, z = load_case("grouped_c4_short")
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, max_seq_len=1024)
+    assert op.variant == 8 and op.query_group == 2
+    out = op.run()
+    torch.cuda.synchronize()
+    from npu_sparse_attn_sharedkv_int8 import c8_attention
+    c8_attention.workspace_status(op)
+    assert_device_band(out.cpu(), op.lse.cpu(), bf16(z["out_g2"]), torch.from_numpy(z["lse_g2"]))
+    again = op.run().clone()
+    torch.cuda.synchronize()
+    assert torch.equal(again, out)
+
+
+def random_sparse_case(seed):
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    g = torch.Generator().manual_seed(9000 + seed)
+    pick = lambda options: options[int(torch.randint(len(options), (1,), generator=g))]
+    batch = int(torch.randint(1, 6, (1,), generator=g))
+    queries = [int(torch.randint(1, 8, (1,), generator=g)) for _ in range(batch)]
+    lengths = [max(q, int(torch.randint(1, 1025, (1,), generator=g))) for q in queries]
+    if seed % 3 == 0:
+        lengths[0] = 1024
+    topk = pick((1024, 256, 64))
+    source = make_case(query_lengths=tuple(queries), seq_lens=tuple(lengths), heads=8, ratio=4, topk=topk, seed=seed)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    idx = case.cmp_indices.clone()
+    style = seed % 4
+    if style == 1:
+        idx[:, :, ::5] = -1                                    # holes
+    elif style == 2:
+        idx[:, :, 3::7] = 2 ** 30                              # out of range
+        idx[:, :, 1::9] = idx[:, :, 0::9][:, :, :idx[:, :, 1::9].shape[-1]]      # duplicates
+    elif style == 3:
+        idx[:, :, topk // 2:] = idx[:, :, :topk - topk // 2]   # every named row named again
+    case = replace(case, cmp_indices=idx.contiguous())
+    stride = pick((16384, PAGE_STRIDE, 16384 + 48))
+    return case, oq.scale, cq.scale, stride, (16 if stride % 512 else 1024)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_grouped_c4_geometry(seed):
+    case, ori_scale, cmp_scale, stride, offset = random_sparse_case(seed)
+    dev = case.to(DEVICE)
+    dev = replace(dev, ori=strided_pages(case.ori, DEVICE, stride, offset), cmp=strided_pages(case.cmp, DEVICE, stride, offset))
+    op = prepared(dev, ori_scale, cmp_scale, max_seq_len=int(case.seq_lens.max()))
+    out = op.run()
+    torch.cuda.synchronize()
+    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=2, return_lse=True)
+    assert_device_band(out.cpu(), op.lse.cpu(), expected, expected_lse)
+
+
+def test_grouped_c4_beyond_its_context_bound_is_reported():
+    """The raw entry on a 2051-token context: the launch completes, the workspace status says
+    SHAREDKV_ERANGE.  (PreparedAttention does not let such a call through.)"""
+    import ctypes
+    from npu_sparse_attn_sharedkv_int8 import c8_attention, runtime
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    case, ori_scale, cmp_scale, _ = load_case("grouped_c4")
+    op = PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE))
+    lib = c8_attention.library()
+    runtime.check(lib.launch_sharedkv_paired_sparse(0, runtime.current_stream(0), ctypes.byref(op.args)), "launch")
+    torch.cuda.synchronize()
+    assert lib.sharedkv_workspace_status(op.workspace.data_ptr(), runtime.current_stream(0)) == -34
+    with pytest.raises(RuntimeError):
+        c8_attention.workspace_status(op)
+
+
 def test_graph_replay_and_a_workspace_shared_with_the_one_token_kernel():
     """A captured graph that launches the one-token kernel and the paired kernel in turn on ONE
     workspace (a serving scratch pool hands the same buffer to launches of different plans): the
@@ -154,8 +227,9 @@ def test_graph_replay_and_a_workspace_shared_with_the_one_token_kernel():
 def test_selection_rules():
     case, ori_scale, cmp_scale, _ = load_case("grouped_c4")
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
-    with pytest.raises(ValueError, match="Query grouping requires"):
-        PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2)
+    for bound in (None, 2051):              # grouped C4 needs a context bound of at most 1024 tokens
+        with pytest.raises(ValueError, match="Query grouping requires"):
+            PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2, max_seq_len=bound)
     case, ori_scale, cmp_scale, _ = load_case("grouped_c128")
     with pytest.raises(ValueError, match="query_group must be"):
         PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=4)
