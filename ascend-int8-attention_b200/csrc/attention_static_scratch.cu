@@ -68,7 +68,8 @@ int scratch_of_current_device(void **address)
 extern "C" int sharedkv_attention_static_scratch(uint32_t variant, void *stream, const SharedKVArgs *args)
 {
     if (args == nullptr) return SHAREDKV_EINVAL;
-    if (variant != SHAREDKV_VARIANT_GENERAL && variant != SHAREDKV_VARIANT_PAIRED && variant != SHAREDKV_VARIANT_PAIRED_SPARSE &&
+    if (variant != SHAREDKV_VARIANT_GENERAL && variant != SHAREDKV_VARIANT_PACKED && variant != SHAREDKV_VARIANT_PACKED_SPARSE &&
+        variant != SHAREDKV_VARIANT_PAIRED && variant != SHAREDKV_VARIANT_PAIRED_SPARSE &&
         variant != SHAREDKV_VARIANT_C4 &&
         variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
         return SHAREDKV_EVARIANT;

@@ -94,6 +94,14 @@ int launch_sharedkv_paired_sparse(uint32_t, void *stream, const SharedKVArgs *ar
 {
     return sharedkv::attention(SHAREDKV_VARIANT_PAIRED_SPARSE, args, static_cast<cudaStream_t>(stream), nullptr);
 }
+int launch_sharedkv_packed(uint32_t, void *stream, const SharedKVArgs *args)
+{
+    return sharedkv::attention(SHAREDKV_VARIANT_PACKED, args, static_cast<cudaStream_t>(stream), nullptr);
+}
+int launch_sharedkv_packed_sparse(uint32_t, void *stream, const SharedKVArgs *args)
+{
+    return sharedkv::attention(SHAREDKV_VARIANT_PACKED_SPARSE, args, static_cast<cudaStream_t>(stream), nullptr);
+}
 int launch_sharedkv_c8_sparse(uint32_t, void *stream, const SharedKVArgs *args)
 {
     return sharedkv::attention(SHAREDKV_VARIANT_C4, args, static_cast<cudaStream_t>(stream), nullptr);

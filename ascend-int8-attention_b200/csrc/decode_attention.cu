@@ -498,13 +498,20 @@ __device__ __noinline__ uint32_t compaction_slot(const Compaction &k, uint32_t s
 
 // ------------------------------------------------------------------ grouped items (paired query tokens)
 // The paired kernel walks two adjacent query tokens of a request as ONE item whose tiles are
-// fetched once and visited by both tokens (reference.py:229-234,243-245 with query_group = 2): the
-// original rows are the union of the two windows, tiled from the union's first row; the compressed
-// rows are the prefix of the later token.  Such an item stores the position of its FIRST token and,
-// in bit 31 of `batch`, whether it holds a second one.
-constexpr uint32_t kPairBit = 0x80000000u;
+// fetched once and used by both tokens (reference.py:229-234,243-245 with query_group = 2 or 4).
+// The tiling belongs to the item's GROUP of two or four tokens: the original rows are the union of
+// the group's windows, tiled from the union's first row; the compressed rows are the prefix of the
+// group's last token.  A group of four is two items that share that tiling.  An item stores the
+// position of its own first token and, in the upper bits of `batch`, what it needs of its group.
+constexpr uint32_t kPairBit = 0x80000000u;              // the item holds a second token
+constexpr uint32_t kPairSecondBit = 0x40000000u;        // the item is the second pair of its group (its first token is the group's third)
+constexpr uint32_t kPairGroupShift = 27;                // bits 27-29: tokens of the group (1..4)
+constexpr uint32_t kPairBatchMask = (1u << kPairGroupShift) - 1u;
 __device__ __forceinline__ uint32_t pair_tokens(uint32_t batch_word) { return (batch_word >> 31) + 1u; }
-__device__ __forceinline__ uint32_t pair_batch(uint32_t batch_word) { return batch_word & ~kPairBit; }
+__device__ __forceinline__ uint32_t pair_batch(uint32_t batch_word) { return batch_word & kPairBatchMask; }
+__device__ __forceinline__ uint32_t group_tokens(uint32_t batch_word) { return (batch_word >> kPairGroupShift) & 7u; }
+// Position of the group's first token, given the position of the item's first token.
+__device__ __forceinline__ int32_t group_position(int32_t position, uint32_t batch_word) { return position - ((batch_word & kPairSecondBit) ? 2 : 0); }
 using split::pair_compressed_rows;
 using split::pair_last_position;
 using split::pair_original_tiles;
@@ -519,16 +526,16 @@ __device__ __forceinline__ int32_t candidate_row(const SharedKVArgs &p, const Cu
 {
     const Item &it = c.it;
     if (GROUP) {
-        const uint32_t tokens = pair_tokens(it.batch);
-        const int32_t last = pair_last_position(it.position, tokens);
+        const uint32_t tokens = group_tokens(it.batch);
+        const int32_t first = group_position(it.position, it.batch), last = pair_last_position(first, tokens);
         if (last < 0) return -1;
-        const uint32_t windows = pair_original_tiles(it.position, tokens);
+        const uint32_t windows = pair_original_tiles(first, tokens);
         if (c.j < windows) {
-            const uint32_t row = pair_window_start(it.position) + c.j * kTileKeys + slot;
+            const uint32_t row = pair_window_start(first) + c.j * kTileKeys + slot;
             return row <= (uint32_t)last ? (int32_t)row : -1;
         }
         const uint32_t s = (c.j - windows) * kTileKeys + slot;
-        return s < pair_compressed_rows(it.position, tokens, p.ratio) ? (int32_t)s : -1;
+        return s < pair_compressed_rows(first, tokens, p.ratio) ? (int32_t)s : -1;
     }
     if (it.position < 0) return -1;
     if (c.j < ori_tiles) {
@@ -631,11 +638,11 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             // ---- stage B: range check and page-table lookup for tile n - kLookahead
             int32_t off_b = -1, page_b = 0;
             if (n >= (uint32_t)kLookahead && !cb.done) {
-                const bool ori = cb.j < (GROUP ? pair_original_tiles(cb.position, pair_tokens(cb.batch)) : ori_tiles);
+                const bool ori = cb.j < (GROUP ? pair_original_tiles(group_position(cb.position, cb.batch), group_tokens(cb.batch)) : ori_tiles);
                 const int32_t c = cand[u];
                 if (GROUP) {
                     // the compressed prefix is that of the group's last token
-                    const uint32_t limit = ori ? 0x7fffffffu : pair_compressed_rows(cb.position, pair_tokens(cb.batch), p.ratio);
+                    const uint32_t limit = ori ? 0x7fffffffu : pair_compressed_rows(group_position(cb.position, cb.batch), group_tokens(cb.batch), p.ratio);
                     const uint32_t request = pair_batch(cb.batch);
                     if (c >= 0 && (uint32_t)c < limit && ((uint32_t)c >> 5) < (ori ? p.oriTableWidth : p.cmpTableWidth)) {
                         off_b = (c & 31) | (ori ? 256 : 0);
@@ -676,7 +683,7 @@ __device__ void producer_loop(const SharedKVArgs &p, const Shared &sm, const Ite
             const uint32_t t = 2u * issued + set;          // position of the tile in the CTA's sequence
             const uint32_t stage = t % STAGES, pass = t / STAGES;
             if (!wait_phase<2>(sm, kBarEmpty + stage, (pass & 1u) ^ 1u)) return;
-            const bool ori = cc.j < (GROUP ? pair_original_tiles(cc.position, pair_tokens(cc.batch)) : ori_tiles);
+            const bool ori = cc.j < (GROUP ? pair_original_tiles(group_position(cc.position, cc.batch), group_tokens(cc.batch)) : ori_tiles);
             const int32_t id = row_ring[u * 32];
             const bool valid = id != kRowsInMap;
             const uint32_t mask = __ballot_sync(0xffffffffu, valid);
@@ -1557,7 +1564,7 @@ int launch(const SharedKVArgs &a, cudaStream_t stream, const SharedKVDebug *debu
 
 // Paired-query C128 launch (decode_paired.cuh): same grid, block and tensor maps as launch() of a ratio-128 layer.
 template <bool TMA>
-cudaError_t launch_decode_paired(const SharedKVArgs &a, const CUtensorMap &ori_map, const CUtensorMap &cmp_map,
+cudaError_t launch_decode_paired(const SharedKVArgs &a, uint32_t group, const CUtensorMap &ori_map, const CUtensorMap &cmp_map,
                                  const CUtensorMap &cmp_page_map, uint32_t grid, cudaStream_t stream, int device)
 {
     static std::atomic<uint64_t> configured{0};
@@ -1578,10 +1585,10 @@ cudaError_t launch_decode_paired(const SharedKVArgs &a, const CUtensorMap &ori_m
     attribute[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attribute;
     config.numAttrs = programmatic_launch_enabled() ? 1u : 0u;
-    return cudaLaunchKernelEx(&config, decode_kernel_paired<TMA>, a, ori_map, cmp_map, cmp_page_map);
+    return cudaLaunchKernelEx(&config, decode_kernel_paired<TMA>, a, group, ori_map, cmp_map, cmp_page_map);
 }
 
-int launch_paired(const SharedKVArgs &a, cudaStream_t stream, int sms)
+int launch_paired(const SharedKVArgs &a, uint32_t group, cudaStream_t stream, int sms)
 {
     const uint32_t grid = (uint32_t)sms < kMaxCtas ? (uint32_t)sms : kMaxCtas;
     int device = 0;
@@ -1594,8 +1601,8 @@ int launch_paired(const SharedKVArgs &a, cudaStream_t stream, int sms)
     if (maps == nullptr) tma = false;
     const CUtensorMap &ori_map = tma ? maps->ori_map : no_map, &cmp_map = tma ? maps->cmp_map : no_map,
                       &cmp_page_map = tma ? maps->cmp_page_map : no_map;
-    e = tma ? launch_decode_paired<true>(a, ori_map, cmp_map, cmp_page_map, grid, stream, device)
-            : launch_decode_paired<false>(a, ori_map, cmp_map, cmp_page_map, grid, stream, device);
+    e = tma ? launch_decode_paired<true>(a, group, ori_map, cmp_map, cmp_page_map, grid, stream, device)
+            : launch_decode_paired<false>(a, group, ori_map, cmp_map, cmp_page_map, grid, stream, device);
     return (int)e;
 }
 
@@ -1616,7 +1623,8 @@ int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, c
 {
     if (args == nullptr) return SHAREDKV_EINVAL;
     const bool general = variant == SHAREDKV_VARIANT_GENERAL;
-    const bool paired = variant == SHAREDKV_VARIANT_PAIRED || variant == SHAREDKV_VARIANT_PAIRED_SPARSE;
+    const bool packed = variant == SHAREDKV_VARIANT_PACKED || variant == SHAREDKV_VARIANT_PACKED_SPARSE;      // groups of four: two pairs share a tiling
+    const bool paired = packed || variant == SHAREDKV_VARIANT_PAIRED || variant == SHAREDKV_VARIANT_PAIRED_SPARSE;
     if (!general && !paired && variant != SHAREDKV_VARIANT_C4 && variant != SHAREDKV_VARIANT_C128 && variant != SHAREDKV_VARIANT_C4_SMALL)
         return SHAREDKV_EVARIANT;
     SharedKVArgs a = *args;
@@ -1624,7 +1632,8 @@ int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, c
     // The C4 / C128 entries take their own ratio and no explicit original slots, as the reference's
     // do; the general entry takes ratio 1 (no compressed cache), 4 or 128, with or without them.
     // The paired entries are the C128 arithmetic, and the grouped C4 walk, with two adjacent query tokens of a request per work item.
-    const uint32_t ratio = general ? a.ratio : ((variant == SHAREDKV_VARIANT_C128 || variant == SHAREDKV_VARIANT_PAIRED) ? 128u : 4u);
+    const uint32_t ratio = general ? a.ratio
+                         : ((variant == SHAREDKV_VARIANT_C128 || variant == SHAREDKV_VARIANT_PAIRED || variant == SHAREDKV_VARIANT_PACKED) ? 128u : 4u);
     if (paired && (debug != nullptr || a.batch + 1u > kPlanStaged)) return SHAREDKV_EINVAL;
     if (a.ratio != ratio || (ratio != 1u && ratio != 4u && ratio != 128u) || (!general && a.oriIndices != 0)) return SHAREDKV_EINVAL;
     if (a.heads != kHeads || a.window != kWindow || a.oriBlock != kPage) return SHAREDKV_EINVAL;
@@ -1651,7 +1660,7 @@ int attention(uint32_t variant, const SharedKVArgs *args, cudaStream_t stream, c
         return SHAREDKV_EINVAL;
     const int sms = device_sm_count();
     if (sms <= 0) return (int)cudaErrorInvalidDevice;
-    if (paired) return launch_paired(a, stream, sms);
+    if (paired) return launch_paired(a, packed ? 4u : 2u, stream, sms);
     return launch(a, stream, debug, sms);
 }
 

@@ -22,6 +22,9 @@
 // tokens, attention.py:89-98) makes that table 256 rows per token.  No explicit original slots (the
 // reference refuses them with groups too).
 //
+// Groups of four (query_group = 4): the tiling is that of the four tokens (union of their windows,
+// prefix of the fourth); the group is two items, each walking the group's tiles for its two tokens.
+//
 // Items are not split between CTAs: an item belongs to the CTA in whose share of the cost list it
 // begins, so there are no partial states and no merges.  The reference's grouped plans are
 // unsplit too (attention.py:121-122: "Grouped-query kernel requires one KV partition").
@@ -54,7 +57,7 @@ constexpr uint32_t kColS2 = 0, kColO2 = 64;
 // ------------------------------------------------------------------ what an item says about its tiles
 struct PairShape {
     uint32_t tokens;        // 1 or 2
-    uint32_t windows;       // original tiles (the window union)
+    uint32_t windows;       // original tiles (the window union of the item's group)
     uint32_t tiles;         // all tiles
     uint32_t kinds;         // 1: original tiles only, 2: compressed tiles as well
 };
@@ -62,7 +65,7 @@ __device__ __forceinline__ PairShape pair_shape(uint32_t batch_word, int32_t fir
 {
     PairShape s;
     s.tokens = pair_tokens(batch_word);
-    s.windows = pair_original_tiles(first_position, s.tokens);
+    s.windows = pair_original_tiles(group_position(first_position, batch_word), group_tokens(batch_word));
     s.tiles = tiles;
     s.kinds = tiles > s.windows ? 2u : 1u;
     return s;
@@ -91,7 +94,7 @@ __device__ __forceinline__ uint32_t owner_of_group(const uint32_t *groups, uint3
     }
     return lo;
 }
-__device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, PairPlanScratch *sc, PlanResult *result)
+__device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t group, const uint32_t grid, PairPlanScratch *sc, PlanResult *result)
 {
     const uint32_t tid = threadIdx.x;
     const int32_t *cu_global = reinterpret_cast<const int32_t *>(p.cuQ);
@@ -141,13 +144,16 @@ __device__ void plan_cta_paired(const SharedKVArgs &p, const uint32_t grid, Pair
     auto describe = [&](uint32_t g) {
         Group d;
         const uint32_t b = owner_of_group(sc->groups, live_batch, g);
-        const uint32_t t0 = (uint32_t)max(sc->cu[b], 0) + 2u * (g - sc->groups[b]);
+        const uint32_t pair = g - sc->groups[b];                  // pair of the request; `group` / 2 pairs share a tiling
+        const uint32_t t0 = (uint32_t)max(sc->cu[b], 0) + 2u * pair;
         const uint32_t last_token = (uint32_t)min(sc->cu[b + 1], (int32_t)live_tokens);
         const uint32_t tokens = min(2u, last_token - t0);
+        const uint32_t second = group == 4u ? pair & 1u : 0u;      // this pair's first token is its group's third
+        const uint32_t in_group = min(group, last_token - (t0 - 2u * second));
         d.token = t0;
         d.position = split::token_position(seq[b], sc->cu[b + 1], t0);
-        d.batch_word = b | (tokens == 2u ? kPairBit : 0u);
-        d.tiles = split::pair_tiles(d.position, tokens, p.ratio);
+        d.batch_word = b | (tokens == 2u ? kPairBit : 0u) | (second ? kPairSecondBit : 0u) | (in_group << kPairGroupShift);
+        d.tiles = split::pair_tiles(d.position - 2 * (int32_t)second, in_group, p.ratio);
         return d;
     };
     uint32_t my_cost = 0;
@@ -433,7 +439,7 @@ __device__ void pair_softmax_loop(const SharedKVArgs &p, const Shared &sm, const
     for (uint32_t k = 0; !cur.done; ++k) {
         const Item it = cur.it;
         const PairShape shape = pair_shape(it);
-        const uint32_t start = pair_window_start(it.position);
+        const uint32_t start = pair_window_start(group_position(it.position, it.batch));
         const float *alphas = reinterpret_cast<const float *>(sm.ptr + kSmAlpha2) + (k & 7u) * 32u;      // [2 tokens][2 kinds][8]
         PairState s0, s1;
 #pragma unroll
@@ -630,7 +636,8 @@ __device__ void pair_accumulate_loop(const SharedKVArgs &p, const Shared &sm, co
 
 // ------------------------------------------------------------------ the paired kernel
 template <bool TMA>
-__global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const SharedKVArgs p, const __grid_constant__ CUtensorMap ori_map,
+__global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const SharedKVArgs p, const uint32_t group,
+                                                                    const __grid_constant__ CUtensorMap ori_map,
                                                                     const __grid_constant__ CUtensorMap cmp_map,
                                                                     const __grid_constant__ CUtensorMap cmp_page_map)
 {
@@ -672,7 +679,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_kernel_paired(const Shared
 
     const char *ws = reinterpret_cast<const char *>(p.workspace);
     const Item *items = reinterpret_cast<const Item *>(ws + kWsItems);
-    plan_cta_paired(p, gridDim.x, reinterpret_cast<PairPlanScratch *>(sm.ptr + kSmKv), reinterpret_cast<PlanResult *>(sm.ptr + kSmPlan));
+    plan_cta_paired(p, group, gridDim.x, reinterpret_cast<PairPlanScratch *>(sm.ptr + kSmKv), reinterpret_cast<PlanResult *>(sm.ptr + kSmPlan));
     const PlanResult &plan = *reinterpret_cast<const PlanResult *>(sm.ptr + kSmPlan);
 
     if (warp < 8) {

@@ -101,16 +101,17 @@ class PreparedAttention:
         self.case, self.scales = case, (ori_scale, cmp_scale)
         self._bind_outputs(output, lse_output, return_lse, tokens, heads, device)
         # 128-key tiles, KV split on the device: the planning keywords of the reference are accepted
-        # only where they say the same.  query_group = 2 (attention.py:96-100,189-190 of the reference)
-        # selects the paired-query C128 kernel: two adjacent tokens of a request share their tiles.
+        # only where they say the same.  query_group = 2 or 4 (attention.py:96-100,186-190 of the reference)
+        # selects the paired-query kernel: two adjacent tokens of a request share their tiles, and a group
+        # of four is two pairs on the group's tiling.
         _require(tile_size in (None, 128), "The CUDA kernels use 128-key tiles; tile_size must be None or 128")
-        _require(query_group in (None, 1, 2), "The CUDA kernels take one or two query tokens per task; query_group must be None, 1 or 2")
+        _require(query_group in (None, 1, 2, 4), "Expected query_group 1, 2 or 4")
         # grouped C4 walks every compressed row of a context, so it is for short contexts only (attention.py:89-98)
         short_c4 = (case.ratio == 4 and isinstance(max_seq_len, int) and 0 < max_seq_len <= 1024
                     and case.cmp_indices is not None and case.cmp_indices.shape[-1] <= 1024)
-        _require(query_group != 2 or (heads == 8 and (case.ratio == 128 or short_c4)),
+        _require(query_group in (None, 1) or (heads == 8 and (case.ratio == 128 or short_c4)),
                  "Query grouping requires eight heads; C4 also requires a max_seq_len bound <= 1024 and top-k <= 1024")
-        _require(query_group != 2 or case.ori_indices is None, "Explicit original slots require ungrouped queries")
+        _require(query_group in (None, 1) or case.ori_indices is None, "Explicit original slots require ungrouped queries")
         _require(splits is None or (isinstance(splits, int) and 1 <= splits <= 24), "Expected 1..24 KV partitions")
         _require(not (adaptive_splits or trim_cube_tails or dynamic_grouped_c128),
                  "Host-selected Ascend tile plans have no CUDA counterpart; leave them unset")

@@ -21,7 +21,7 @@ DIM = 512
 MAX_SPLITS = CORES          # a token's KV may be spread over at most one piece per CTA
 _MAX_CTAS = 160             # partial-result slots the library reserves
 _PARTIAL_FLOATS = HEADS * DIM + 16
-_VARIANTS = {"general": 0, "paired": 7, "paired_sparse": 8, "sparse": 20, "dense": 21, "sparse_small": 22}     # kernel ids of the host bridge
+_VARIANTS = {"general": 0, "packed": 3, "packed_sparse": 4, "paired": 7, "paired_sparse": 8, "sparse": 20, "dense": 21, "sparse_small": 22}     # kernel ids of the host bridge
 _PAIRED_MAX_BATCH = 11775   # requests whose cumulative counts the paired kernel keeps in shared memory
 _SMALL_C4_TOKENS = 24       # below this the reference selects its "small" C4 image (c4_small.cpp:21)
 
@@ -74,14 +74,14 @@ def supported(entry):
         return False
     if (args.heads, args.window, args.oriBlock) != (HEADS, 128, 32) or (args.ratio != 1 and args.cmpBlock != 32):
         return False
-    if getattr(entry, "query_group", 1) == 2 and (args.ratio not in (4, 128) or args.oriIndices or args.batch > _PAIRED_MAX_BATCH):
+    if getattr(entry, "query_group", 1) in (2, 4) and (args.ratio not in (4, 128) or args.oriIndices or args.batch > _PAIRED_MAX_BATCH):
         return False
     return args.ratio in (1, 128) or (args.ratio == 4 and 0 < args.topk <= 1024)
 
 
 def _launcher_name(args, query_group=1):
-    if query_group == 2:
-        return "paired" if args.ratio == 128 else "paired_sparse"
+    if query_group in (2, 4):
+        return ("paired" if query_group == 2 else "packed") + ("" if args.ratio == 128 else "_sparse")
     if args.ratio == 1 or args.oriIndices:
         return "general"
     if args.ratio == 128:
@@ -127,8 +127,8 @@ def prepare(entry, *, scratch_allocator=None, shared_storage=False):
     bound.argument_address = ctypes.addressof(bound.args)
     name = _launcher_name(bound.args, getattr(bound, "query_group", 1))
     bound._c8_library = library()
-    bound.launch = getattr(bound._c8_library, {"general": "launch_sharedkv", "paired": "launch_sharedkv_paired",
-                                               "paired_sparse": "launch_sharedkv_paired_sparse"}.get(name, "launch_sharedkv_c8_" + name))
+    bound.launch = getattr(bound._c8_library, "launch_sharedkv" if name == "general" else
+                           "launch_sharedkv_" + name if name.startswith(("paired", "packed")) else "launch_sharedkv_c8_" + name)
     bound.variant = _VARIANTS[name]
     bound.native = native_host(os.environ.get("SHAREDKV_HOST_QUEUE") == "1")
     if bound.native is not None and bound.native.attention_args_size != ctypes.sizeof(type(bound.args)):

@@ -33,7 +33,7 @@ def _library():
     for name in ("sharedkv_attention_args_size", "sharedkv_cache_args_size", "sharedkv_attention_variant_count"):
         getattr(lib, name).argtypes, getattr(lib, name).restype = [], u32
     lib.sharedkv_workspace_bytes.argtypes, lib.sharedkv_workspace_bytes.restype = [u32], u64
-    for name in ("launch_sharedkv", "launch_sharedkv_paired", "launch_sharedkv_paired_sparse", "launch_sharedkv_c8_sparse", "launch_sharedkv_c8_sparse_small", "launch_sharedkv_c8_dense",
+    for name in ("launch_sharedkv", "launch_sharedkv_paired", "launch_sharedkv_paired_sparse", "launch_sharedkv_packed", "launch_sharedkv_packed_sparse", "launch_sharedkv_c8_sparse", "launch_sharedkv_c8_sparse_small", "launch_sharedkv_c8_dense",
                  "launch_cache_write"):
         getattr(lib, name).argtypes, getattr(lib, name).restype = [u32, ptr, ptr], ctypes.c_int
     lib.sharedkv_attention.argtypes, lib.sharedkv_attention.restype = [u64, u32, u32, i32, ptr], ctypes.c_int

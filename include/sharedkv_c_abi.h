@@ -102,9 +102,10 @@ enum {
 };
 
 /* Kernel variants of the host bridge: 0 is the reference's general 128-key-tile kernel
- * (launch.cpp:33), 7 and 8 its paired-query C128 and C4 kernels (launch.cpp:40-41), 20-22 its C4 / C128 decode
+ * (launch.cpp:33), 3 / 4 and 7 / 8 its grouped-query C128 / C4 kernels for groups of four and two
+ * (launch.cpp:36-37,40-41), 20-22 its C4 / C128 decode
  * kernels (c8_launch.cpp:12-18). */
-enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_PAIRED = 7, SHAREDKV_VARIANT_PAIRED_SPARSE = 8, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
+enum { SHAREDKV_VARIANT_GENERAL = 0, SHAREDKV_VARIANT_PACKED = 3, SHAREDKV_VARIANT_PACKED_SPARSE = 4, SHAREDKV_VARIANT_PAIRED = 7, SHAREDKV_VARIANT_PAIRED_SPARSE = 8, SHAREDKV_VARIANT_C4 = 20, SHAREDKV_VARIANT_C128 = 21, SHAREDKV_VARIANT_C4_SMALL = 22 };
 
 /* sizeof(SharedKVArgs) / sizeof(CacheWriteArgs) as compiled into the library; the
  * Python layer compares them with its ctypes mirrors (attention.py:223-226,
@@ -162,6 +163,13 @@ SHAREDKV_API int launch_sharedkv_paired(uint32_t blocks, void *stream, const Sha
  * compressed row are not attended.  Replaces csrc/kernels/sharedkv_paired_sparse.cpp:7
  * (`launch_sharedkv_paired_sparse`, variant 8 of launch.cpp:41). */
 SHAREDKV_API int launch_sharedkv_paired_sparse(uint32_t blocks, void *stream, const SharedKVArgs *args);
+/* Groups of four adjacent query tokens (query_group = 4 of the reference): the tiling of the window
+ * rows and the compressed prefix belongs to the group of four, as in the reference's arithmetic; the
+ * group is walked as two pairs, each fetching the group's tiles for its two tokens.  Otherwise as the
+ * paired entries.  Replace `launch_sharedkv_packed` / `launch_sharedkv_packed_sparse` (variants 3
+ * and 4 of launch.cpp:36-37). */
+SHAREDKV_API int launch_sharedkv_packed(uint32_t blocks, void *stream, const SharedKVArgs *args);
+SHAREDKV_API int launch_sharedkv_packed_sparse(uint32_t blocks, void *stream, const SharedKVArgs *args);
 
 /* C4 (ratio 4): window of <=128 original rows + <=1024 selected compressed rows per
  * query token.  `blocks` is accepted for signature compatibility and ignored: the

@@ -1,7 +1,8 @@
 // Host-compiled check of the paired kernel's work split and tiling (csrc/work_split.h: pair_*),
 // the arithmetic plan_cta_paired and the producers of decode_kernel_paired run on the device.
-// Over random chunked-prefill workloads: every live query token is in exactly one item, an item
-// holds one or two adjacent tokens of one request, the items of a CTA are consecutive workspace
+// Over random chunked-prefill workloads (groups of two and of four tokens, ratio 128 and the grouped
+// C4 walk): every live query token is in exactly one item, an item holds one or two adjacent tokens of
+// one request and takes its tiling from its group, the items of a CTA are consecutive workspace
 // entries, every item has an owner below the grid, the tiles of an item cover exactly the rows its
 // tokens may see (reference.py:229-234,243-245 with query_group = 2), and nobody is given more
 // than its quota plus one item.
@@ -20,7 +21,7 @@ using namespace sharedkv::split;
 #define REQUIRE(cond)                                                                                            \
     do {                                                                                                         \
         if (!(cond)) {                                                                                           \
-            std::fprintf(stderr, "workload %u (ratio %u, grid %u, batch %u): %s failed at line %d\n", trial, ratio, grid, batch, #cond, __LINE__); \
+            std::fprintf(stderr, "workload %u (ratio %u, group %u, grid %u, batch %u): %s failed at line %d\n", trial, ratio, group, grid, batch, #cond, __LINE__); \
             return 1;                                                                                            \
         }                                                                                                        \
     } while (0)
@@ -34,6 +35,7 @@ int main(int argc, char **argv)
     for (unsigned trial = 0; trial < workloads; ++trial) {
         const uint32_t grid = trial % 7 == 0 ? uniform(1, 4) : uniform(1, kMaxCtas);
         const uint32_t ratio = trial % 3 == 2 ? 4u : 128u;          // 4: the grouped C4 walk over a short context
+        const uint32_t group = trial % 2 ? 4u : 2u;                 // tokens whose tiling an item shares: its own pair, or two pairs
         const uint32_t shape = rng() % 8;
         const uint32_t batch = shape == 0 ? uniform(1, 3000) : shape < 4 ? uniform(1, 8) : uniform(1, 200);
         const uint32_t max_queries = shape == 0 ? 3 : (rng() % 3 == 0 ? 600 : 9);
@@ -52,8 +54,8 @@ int main(int argc, char **argv)
 
         // the plan: groups per request, cost of every group, owner by the cost in front of it
         struct Group {
-            uint32_t batch, token, tokens, tiles, owner;
-            int32_t position;
+            uint32_t batch, token, tokens, tiles, owner, group_tokens;
+            int32_t position, group_position;
         };
         std::vector<Group> groups;
         for (uint32_t b = 0; b < batch; ++b) {
@@ -64,7 +66,11 @@ int main(int argc, char **argv)
                 d.token = (uint32_t)cu[b] + 2u * g;
                 d.tokens = std::min(2u, (uint32_t)cu[b + 1] - d.token);
                 d.position = token_position(seq[b], cu[b + 1], d.token);
-                d.tiles = pair_tiles(d.position, d.tokens, ratio);
+                // the tiling belongs to the group: the pair itself, or the two pairs of four tokens
+                const uint32_t second = group == 4u ? g & 1u : 0u;
+                d.group_position = d.position - 2 * (int32_t)second;
+                d.group_tokens = std::min(group, (uint32_t)cu[b + 1] - (d.token - 2u * second));
+                d.tiles = pair_tiles(d.group_position, d.group_tokens, ratio);
                 groups.push_back(d);
             }
         }
@@ -100,12 +106,13 @@ int main(int argc, char **argv)
         // tiling of a sample of items: the rows each token sees are exactly those the tiles offer it
         for (size_t g = 0; g < groups.size(); g += 1 + groups.size() / 64) {
             const Group &d = groups[g];
-            const uint32_t windows = pair_original_tiles(d.position, d.tokens);
+            const uint32_t windows = pair_original_tiles(d.group_position, d.group_tokens);
             REQUIRE(windows == 1 || windows == 2);
             two_window_tiles += windows == 2;
-            const uint32_t start = pair_window_start(d.position);
-            const int32_t last = pair_last_position(d.position, d.tokens);
-            const uint32_t compressed = pair_compressed_rows(d.position, d.tokens, ratio);
+            const uint32_t start = pair_window_start(d.group_position);
+            const int32_t last = pair_last_position(d.group_position, d.group_tokens);
+            const uint32_t compressed = pair_compressed_rows(d.group_position, d.group_tokens, ratio);
+            REQUIRE(d.group_tokens >= d.tokens && d.group_tokens <= group && d.position + (int32_t)d.tokens - 1 <= last);
             REQUIRE(d.tiles == windows + (compressed + kTileKeys - 1) / kTileKeys);
             for (uint32_t i = 0; i < d.tokens; ++i) {
                 const int32_t position = d.position + (int32_t)i;

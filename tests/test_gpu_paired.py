@@ -21,9 +21,9 @@ pytestmark = pytest.mark.gpu
 DEVICE = "cuda:0"
 
 
-def prepared(case, ori_scale, cmp_scale, **kw):
+def prepared(case, ori_scale, cmp_scale, group=2, **kw):
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
-    return PreparedAttention(case, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2, return_lse=True, **kw)
+    return PreparedAttention(case, ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=group, return_lse=True, **kw)
 
 
 def assert_device_band(out, lse, expected, expected_lse):
@@ -46,6 +46,17 @@ def test_golden_grouped_case():
     again = op.run().clone()
     torch.cuda.synchronize()
     assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("name,bound,variant", [("grouped_c128", None, 3), ("grouped_c4_short", 1024, 4)])
+def test_golden_cases_in_groups_of_four(name, bound, variant):
+    """query_group = 4: the tiling of four adjacent tokens, walked as two pairs."""
+    case, ori_scale, cmp_scale, z = load_case(name)
+    op = prepared(to_device(case, DEVICE), ori_scale, cmp_scale, group=4, max_seq_len=bound)
+    assert op.variant == variant and op.query_group == 4
+    out = op.run()
+    torch.cuda.synchronize()
+    assert_device_band(out.cpu(), op.lse.cpu(), bf16(z["out_g4"]), torch.from_numpy(z["lse_g4"]))
 
 
 def random_case(seed):
@@ -74,10 +85,11 @@ def test_random_geometry(seed):
     case, ori_scale, cmp_scale, stride, offset = random_case(seed)
     dev = case.to(DEVICE)
     dev = replace(dev, ori=strided_pages(case.ori, DEVICE, stride, offset), cmp=strided_pages(case.cmp, DEVICE, stride, offset))
-    op = prepared(dev, ori_scale, cmp_scale)
+    group = 4 if seed % 2 else 2
+    op = prepared(dev, ori_scale, cmp_scale, group=group)
     out = op.run()
     torch.cuda.synchronize()
-    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=2, return_lse=True)
+    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=group, return_lse=True)
     assert_device_band(out.cpu(), op.lse.cpu(), expected, expected_lse)
 
 
@@ -152,10 +164,11 @@ def test_random_grouped_c4_geometry(seed):
     case, ori_scale, cmp_scale, stride, offset = random_sparse_case(seed)
     dev = case.to(DEVICE)
     dev = replace(dev, ori=strided_pages(case.ori, DEVICE, stride, offset), cmp=strided_pages(case.cmp, DEVICE, stride, offset))
-    op = prepared(dev, ori_scale, cmp_scale, max_seq_len=int(case.seq_lens.max()))
+    group = 4 if seed % 2 else 2
+    op = prepared(dev, ori_scale, cmp_scale, group=group, max_seq_len=int(case.seq_lens.max()))
     out = op.run()
     torch.cuda.synchronize()
-    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=2, return_lse=True)
+    expected, expected_lse = oracle.attention_tiled(case, ori_scale, cmp_scale, query_group=group, return_lse=True)
     assert_device_band(out.cpu(), op.lse.cpu(), expected, expected_lse)
 
 
@@ -231,5 +244,5 @@ def test_selection_rules():
         with pytest.raises(ValueError, match="Query grouping requires"):
             PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=2, max_seq_len=bound)
     case, ori_scale, cmp_scale, _ = load_case("grouped_c128")
-    with pytest.raises(ValueError, match="query_group must be"):
-        PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=4)
+    with pytest.raises(ValueError, match="Expected query_group"):
+        PreparedAttention(to_device(case, DEVICE), ori_scale.to(DEVICE), cmp_scale.to(DEVICE), query_group=3)
