@@ -108,7 +108,7 @@ def pair_bytes(lengths):
 def workload_label(args):
     return {"box": f"box-scale decode step: {args.requests} requests, ctx log-uniform 4k-1M, alternating C4/C128",
             "c128": f"C128 decode, B=64, T={args.queries}, ctx U[8k,128k], compact pages (stride 38 x 16384 B, offset 16384 B)"
-                    + (", paired queries" if args.query_group == 2 else ""),
+                    + (f", query groups of {args.query_group}" if args.query_group > 1 else ""),
             "c4mtp": "C4 decode with MTP, B=256, T=2, ctx U[32k,128k], top-k 1024 + window 128",
             "writer": "paged INT8 cache writer: 65536 BF16 rows -> original cache + 16384 rows -> ratio-4 compressed cache, random slots"
             }[args.workload]
@@ -627,8 +627,9 @@ def main():
                         help="box workload: layer kinds per pair (one kind keeps a profiler capture small)")
     parser.add_argument("--rotate", type=int, default=8, help="cache copies rotated through by the small workloads")
     parser.add_argument("--queries", type=int, default=1, help="query tokens per request of the c128 workload (chunked-prefill shapes)")
-    parser.add_argument("--query-group", type=int, default=1, choices=(1, 2),
-                        help="2: the c128 workload runs the paired-query kernel (two adjacent tokens of a request per work item)")
+    parser.add_argument("--query-group", type=int, default=1, choices=(1, 2, 4),
+                        help="2 or 4: the c128 workload runs the paired-query kernel (two adjacent tokens of a request per work "
+                             "item; 4: two such items on the tiling of four tokens)")
     parser.add_argument("--passes", type=int, default=0,
                         help="decode passes per step; 0 = as many as make the timed steps last --seconds")
     parser.add_argument("--seconds", type=float, default=2.5, help="length aimed at for the timed region when --passes is 0")
@@ -664,7 +665,7 @@ def main():
 
     work, label = build_workload(args, rank, world)
     layers = len(work.layers)
-    grouping = {"query_group": 2} if args.query_group == 2 and args.workload == "c128" else {}
+    grouping = {"query_group": args.query_group} if args.query_group > 1 and args.workload == "c128" else {}
     ops = [PreparedAttention(work.case(i), work.layers[i].ori_scale, work.layers[i].cmp_scale, **grouping) for i in range(layers)]
     rows_per_layer = [work.kv_rows(i) for i in range(layers)]
     # a pass: every resident layer once (box), or one launch on the next of the rotating copies (single-layer workloads)
