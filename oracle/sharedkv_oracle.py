@@ -208,7 +208,7 @@ class Trace:
 
 
 def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1, query_group=1,
-                    return_lse=False, trace: Trace | None = None, tile_parts=None):
+                    return_lse=False, trace: Trace | None = None, tile_parts=None, only_tokens=None):
     """Online-softmax INT8 attention, tile by tile   (reference.py:210-323).
 
     Tiles are numbered original-first then compressed and dealt round-robin
@@ -219,10 +219,16 @@ def attention_tiled(case, ori_scale, cmp_scale=None, *, tile_size=128, splits=1,
     round-robin deal by an explicit one, so that the oracle can follow a device
     that cuts a token's tiles into contiguous pieces; tiles beyond the list go to
     the last state named.  The merge formula is the same.
+
+    `only_tokens` (a collection of query token numbers) restricts the walk to those tokens, in
+    increasing order; the results then have one row per listed token (sampling a large launch).
     """
     heads = case.q.shape[1]
     outputs, lses = [], []
+    wanted = None if only_tokens is None else set(int(t) for t in only_tokens)
     for batch, token in tokens_of(case):
+        if wanted is not None and token not in wanted:
+            continue
         sel = select(case, batch, token, query_group)
         groups = [(case.ori, case.ori_block_table, sel.ori_index, sel.ori_valid, ori_scale)]
         if case.ratio != 1:

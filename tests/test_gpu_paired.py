@@ -116,6 +116,39 @@ def test_chunked_prefill_chunk_with_a_dead_request():
     assert not out[81:].any() and not op.lse[81:].any()
 
 
+@pytest.mark.parametrize("tokens,length", [(4096, 65536), (16384, 16384)])
+def test_prefill_capacity(tokens, length):
+    """One request with as many query tokens as the reference serves on one core (tests/npu/
+    test_capacity.py:41-51 of the reference: chunk4096_long, prefill16384): the one-token walk, pairs and
+    groups of four against the oracle on 24 sampled tokens each (device band for the grouped
+    plans, acceptance band for the one-token walk, whose pieces the sample does not follow), and
+    against one another on every token (acceptance band)."""
+    from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    source = make_case(query_lengths=(tokens,), seq_lens=(length,), heads=8, ratio=128, topk=1024, seed=tokens)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    dev = case.to(DEVICE)
+    g = torch.Generator().manual_seed(1)
+    sample = sorted(set([0, 1, 2, 3, 126, 127, 128, 129, tokens - 2, tokens - 1] + torch.randint(0, tokens, (14,), generator=g).tolist()))
+    outputs = {}
+    for group in (1, 2, 4):
+        op = PreparedAttention(dev, oq.scale.to(DEVICE), cq.scale.to(DEVICE), query_group=group, return_lse=True)
+        out = op.run()
+        torch.cuda.synchronize()
+        outputs[group] = out.cpu().float()
+        expected, expected_lse = oracle.attention_tiled(case, oq.scale, cq.scale, query_group=group, return_lse=True, only_tokens=sample)
+        if group == 1:
+            m = error_metrics(outputs[group][sample], expected.float())
+            assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+            torch.testing.assert_close(op.lse.cpu()[sample], expected_lse, rtol=1e-4, atol=1e-4)
+        else:
+            assert_device_band(out.cpu()[sample], op.lse.cpu()[sample], expected, expected_lse)
+    for group in (2, 4):
+        m = error_metrics(outputs[group], outputs[1])
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, (group, m)
+
+
 def test_golden_grouped_c4_case_with_duplicate_selections():
     """Contexts of 700, 1024, 131 and 9 tokens, 5 + 2 + 3 + 1 query tokens, top-k lists that name some
     rows two and three times (and so drop others)."""

@@ -181,6 +181,55 @@ def test_twelve_thousand_requests_in_one_launch(ratio):
     assert torch.isfinite(out.float()).all()
 
 
+@pytest.mark.parametrize("ratio", (4, 128))
+@pytest.mark.parametrize("batch,queries", [(65, 1), (513, 1), (65, 5)])
+@pytest.mark.parametrize("offset", (1, 15))
+def test_metadata_views_at_odd_offsets(ratio, batch, queries, offset):
+    """seqLens and cuQ as views 4 and 60 bytes into larger INT32 tensors (the reference's
+    tests/npu/test_metadata_views.py:20-57: batches of 65 and 513, one and five query tokens, contexts
+    of a few tokens): a captured launch replayed three times over a poisoned workspace, results
+    against the oracle, the words around the views untouched."""
+    from npu_sparse_attn_sharedkv_int8.reference import CacheQuantization, make_case
+    length = max(3, queries) if ratio == 4 else 127
+    source = make_case(query_lengths=(queries,) * batch, seq_lens=(length,) * batch, heads=8, ratio=ratio, topk=1024,
+                       seed=batch + queries + offset)
+    oq, cq = CacheQuantization.calibrate([source.ori]), CacheQuantization.calibrate([source.cmp])
+    case = replace(source, ori=oq.quantize(source.ori), cmp=cq.quantize(source.cmp))
+    dev = case.to(DEVICE)
+    storage = []
+    for name in ("seq_lens", "cu_q"):
+        original = getattr(dev, name)
+        raw = torch.full((offset + original.numel() + 16,), -777, dtype=torch.int32, device=DEVICE)
+        view = raw[offset:offset + original.numel()]
+        view.copy_(original)
+        dev = replace(dev, **{name: view})
+        storage.append((raw, original.numel()))
+    op = prepared(dev, oq.scale, cq.scale, return_lse=True)
+    assert op.args.seqLens % 16 != 0 and op.args.cuQ % 16 != 0
+    initial = bytes(op.args)
+    op.run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    stream = torch.cuda.Stream(device=DEVICE)
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            op.run()
+    torch.cuda.synchronize()
+    expected, expected_lse = oracle.attention_tiled(case, oq.scale, cq.scale, return_lse=True)
+    for _ in range(3):
+        op.workspace[1024:].fill_(0xA5)
+        op.out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        m = error_metrics(op.out.cpu().float(), expected.float())
+        assert m["max_abs"] <= 2e-2 and m["mean_abs"] <= 2e-3, m
+        torch.testing.assert_close(op.lse.cpu(), expected_lse, rtol=1e-4, atol=1e-4)
+        assert bytes(op.args) == initial
+    for raw, size in storage:
+        assert (raw[:offset] == -777).all() and (raw[offset + size:] == -777).all()
+
+
 def test_two_streams_at_once():
     """Two prepared operators with their own workspaces, launched back to back on two streams so
     that their persistent kernels compete for the SMs: no CTA ever waits for another CTA, so the
