@@ -23,7 +23,7 @@ DEVICE = "cuda:0"
 SAMPLED = 20
 
 
-def run_and_compare(work, layer_index=0):
+def run_and_compare(work, layer_index=0, sampled=SAMPLED):
     from npu_sparse_attn_sharedkv_int8 import synthetic
     from npu_sparse_attn_sharedkv_int8.attention import PreparedAttention
     layer = work.layers[layer_index]
@@ -36,9 +36,9 @@ def run_and_compare(work, layer_index=0):
 
     # shortest, longest and a spread of the requests in between
     order = torch.argsort(work.seq_lens_host).tolist()
-    step = max(1, len(order) // (SAMPLED - 2))
-    sample = sorted(set(order[::step][:SAMPLED - 2]) | {order[0], order[-1]})
-    assert len(sample) >= 16
+    step = max(1, len(order) // (sampled - 2))
+    sample = sorted(set(order[::step][:sampled - 2]) | {order[0], order[-1]})
+    assert len(sample) >= min(16, sampled - 2, len(order))
     small, ori_scale, cmp_scale, ids = synthetic.extract_requests(work, layer_index, sample)
     got, got_lse = out[ids.to(DEVICE)].cpu().float(), lse[ids.to(DEVICE)].cpu()
 
