@@ -27,7 +27,7 @@
 //
 // Items are not split between CTAs: an item belongs to the CTA in whose share of the cost list it
 // begins, so there are no partial states and no merges.  The reference's grouped plans are
-// unsplit too (attention.py:121-122: "Grouped-query kernel requires one KV partition").
+// unsplit too (attention.py:112-113: "Grouped-query kernel requires one KV partition").
 //
 // Shared memory: the 32-row query codes (16 KB a set) and the 32-column P codes do not fit beside
 // three 64 KB key tiles, so the key ring has two stages and the third stage's 64 KB hold them.  The
